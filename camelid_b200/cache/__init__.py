@@ -1,6 +1,6 @@
-from .book import PAGE, CacheBook, FreeList, KVSpec, StateSpec
+from .book import PAGE, CacheBook, FreeList, KVSpec, StateSpec, flatten_specs
 
-__all__ = ["PAGE", "CacheBook", "FreeList", "KVSpec", "StateSpec", "SequenceCache"]
+__all__ = ["PAGE", "CacheBook", "FreeList", "KVSpec", "StateSpec", "SequenceCache", "flatten_specs"]
 
 
 def __getattr__(name):

@@ -25,18 +25,34 @@ PAGE = 64
 @dataclass(frozen=True)
 class KVSpec:
     """Keys and values per position: ``window`` None keeps all of them, an integer keeps the
-    last ``window`` positions."""
+    last ``window`` positions. ``v_head_dim`` (None: ``head_dim``) is the size of a value."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
 class StateSpec:
     """State of fixed size per sequence: a tensor of ``shape`` and ``dtype`` for every slot,
-    zeroed when the slot is handed out."""
+    zeroed when the slot is handed out. A schedule entry that keeps several states tells them
+    apart by ``name``."""
     shape: tuple
     dtype: str = "float32"
+    name: str = ""
+
+
+def flatten_specs(spec) -> list:
+    """What a schedule entry asks of the cache as a flat list: None, one spec, or a (nested) list of them."""
+    if spec is None:
+        return []
+    if isinstance(spec, (list, tuple)):
+        return [x for s in spec for x in flatten_specs(s)]
+    return [spec]
 
 
 class FreeList:

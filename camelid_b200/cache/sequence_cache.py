@@ -1,7 +1,7 @@
 """The cache on the device: page pools for keys and values, and fixed-size state per slot.
 
-Each schedule entry of the model states what its mixer needs (a ``KVSpec``, a
-``StateSpec`` or nothing). Entries with equal ``KVSpec`` share one group: one tensor
+Each schedule entry of the model states what its parts need (a ``KVSpec``, a
+``StateSpec``, a list of them with at most one ``KVSpec`` and states of different names, or nothing). Entries with equal ``KVSpec`` share one group: one tensor
 ``[entries, pages, kv_heads, 64, head_dim]`` for keys and one for values, in the compute
 type, and one page pool. Entries with equal ``StateSpec`` share one tensor
 ``[entries, slots, *shape]``. An entry that reads another entry's cache has no storage.
@@ -18,7 +18,7 @@ from typing import Optional
 import torch
 
 from ..errors import CacheError
-from .book import PAGE, CacheBook, KVSpec, StateSpec
+from .book import PAGE, CacheBook, KVSpec, StateSpec, flatten_specs
 
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
 
@@ -41,22 +41,29 @@ class SequenceCache:
         for i, (spec, src) in enumerate(zip(entry_specs, entry_sources)):
             if src is not None:
                 continue
-            if isinstance(spec, KVSpec):
-                if spec not in kv_specs:
-                    kv_specs.append(spec)
-                    counts_kv.append(0)
-                g = kv_specs.index(spec)
-                self.entry_kv[i] = (g, counts_kv[g])
-                counts_kv[g] += 1
-            elif isinstance(spec, StateSpec):
-                if spec not in state_specs:
-                    state_specs.append(spec)
-                    counts_state.append(0)
-                g = state_specs.index(spec)
-                self.entry_state[i] = (g, counts_state[g])
-                counts_state[g] += 1
-            elif spec is not None:
-                raise CacheError(f"schedule entry {i}: unknown cache need {spec!r}")
+            for one in flatten_specs(spec):
+                if isinstance(one, KVSpec):
+                    if self.entry_kv[i] is not None:
+                        raise CacheError(f"schedule entry {i} asks for two sets of keys and values")
+                    if one not in kv_specs:
+                        kv_specs.append(one)
+                        counts_kv.append(0)
+                    g = kv_specs.index(one)
+                    self.entry_kv[i] = (g, counts_kv[g])
+                    counts_kv[g] += 1
+                elif isinstance(one, StateSpec):
+                    if self.entry_state[i] is None:
+                        self.entry_state[i] = {}
+                    if one.name in self.entry_state[i]:
+                        raise CacheError(f"schedule entry {i} keeps two states named {one.name!r}")
+                    if one not in state_specs:
+                        state_specs.append(one)
+                        counts_state.append(0)
+                    g = state_specs.index(one)
+                    self.entry_state[i][one.name] = (g, counts_state[g])
+                    counts_state[g] += 1
+                else:
+                    raise CacheError(f"schedule entry {i}: unknown cache need {one!r}")
         for i, src in enumerate(entry_sources):
             if src is not None:
                 if self.entry_kv[src] is None:
@@ -71,7 +78,8 @@ class SequenceCache:
         # zero-filled once; kernels never count rows beyond a sequence's length
         self.k = [torch.zeros((counts_kv[g], n_pages, s.n_kv_heads, PAGE, s.head_dim), dtype=dtype, device=self.device)
                   for g, s in enumerate(kv_specs)]
-        self.v = [torch.zeros_like(t) for t in self.k]
+        self.v = [torch.zeros((counts_kv[g], n_pages, s.n_kv_heads, PAGE, s.value_dim), dtype=dtype, device=self.device)
+                  for g, s in enumerate(kv_specs)]
         self.state = [torch.zeros((counts_state[g], n_slots) + tuple(s.shape), dtype=_STATE_DTYPES[s.dtype],
                                   device=self.device) for g, s in enumerate(state_specs)]
         self.bytes = need
@@ -81,7 +89,7 @@ class SequenceCache:
         size = torch.empty((), dtype=dtype).element_size()
         total = 0
         for s, c in zip(kv_specs, counts_kv):
-            total += 2 * c * n_pages * s.n_kv_heads * PAGE * s.head_dim * size
+            total += c * n_pages * s.n_kv_heads * PAGE * (s.head_dim + s.value_dim) * size
         for s, c in zip(state_specs, counts_state):
             n = 1
             for d in s.shape:
@@ -120,10 +128,16 @@ class SequenceCache:
         g, i = where
         return g, self.k[g][i], self.v[g][i]
 
-    def state_of(self, entry: int) -> torch.Tensor:
-        """[slots, *shape] state of a schedule entry."""
+    def state_of(self, entry: int, name: str | None = None) -> torch.Tensor:
+        """[slots, *shape] state of a schedule entry; ``name`` picks one where the entry keeps several."""
         where = self.entry_state[entry]
         if where is None:
             raise CacheError(f"schedule entry {entry} keeps no per-sequence state")
-        g, i = where
+        if name is None:
+            if len(where) != 1:
+                raise CacheError(f"schedule entry {entry} keeps the states {sorted(where)}: name one")
+            name = next(iter(where))
+        if name not in where:
+            raise CacheError(f"schedule entry {entry} keeps no state named {name!r} (it keeps {sorted(where)})")
+        g, i = where[name]
         return self.state[g][i]

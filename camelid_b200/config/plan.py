@@ -25,12 +25,15 @@ class PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One layer: the arrangement of its parts (``prenorm``: x + mixer(norm(x)), then
-    r + ffn(norm(r))) and the parts themselves. Layers of one model may differ."""
+    r + ffn(norm(r))) and the parts themselves. Layers of one model may differ. A layer
+    without ``ffn`` (and ``norm2``) has only the first sublayer; ``shift`` names a part that
+    stands between the first norm and the mixer (a token shift)."""
     arrangement: str
     norm1: PartSpec
     mixer: PartSpec
-    norm2: PartSpec
-    ffn: PartSpec
+    norm2: Optional[PartSpec] = None
+    ffn: Optional[PartSpec] = None
+    shift: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -38,9 +41,12 @@ class ScheduleEntry:
     """One run of a layer. ``layer`` indexes ``ModelPlan.layers`` and may occur in several
     entries (the layer's weights are then shared, each entry keeping a cache of its own).
     ``cache_source`` names an earlier entry of the schedule whose keys and values this
-    entry reads instead of making its own."""
+    entry reads instead of making its own. ``pass_number`` t marks the first layer of the
+    t-th pass over a stretch of layers that runs several times: the plan's ``pass_input`` part
+    runs right before it."""
     layer: int
     cache_source: Optional[int] = None
+    pass_number: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -54,9 +60,12 @@ class ModelPlan:
     vocab_size: int
     max_position: int
     stop_token_ids: tuple = ()
+    pass_input: Optional[PartSpec] = None       # what happens to the stream before each pass of a looped stretch
 
     def __post_init__(self):
         for i, e in enumerate(self.schedule):
+            if e.pass_number is not None and self.pass_input is None:
+                raise ConfigError("schedule", f"schedule entry {i} starts pass {e.pass_number} but the plan has no pass_input part")
             if not 0 <= e.layer < len(self.layers):
                 raise ConfigError("schedule", f"schedule entry {i} names layer {e.layer}, the plan has {len(self.layers)}")
             if e.cache_source is not None:

@@ -37,8 +37,11 @@ def known_architectures() -> list[str]:
 
 def architecture_of(config_dict: dict) -> Architecture:
     archs = config_dict.get("architectures")
+    if archs is None and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]           # some designs name themselves with one string
     if not archs or not isinstance(archs, list):
-        raise ConfigError("architectures", "required key is missing (a list with the model class name)")
+        raise ConfigError("architectures", "required key is missing (a list with the model class name, or "
+                          "'architecture' with one name)")
     for name in archs:
         if name in _ARCHITECTURES:
             return _ARCHITECTURES[name]
@@ -66,7 +69,7 @@ def load_config(folder_or_dict):
 
 
 # ---------------------------------------------------------------------------------------
-# the one architecture of this library
+# the architectures of this library
 
 
 def llama_plan(cfg: LlamaConfig) -> ModelPlan:
@@ -117,3 +120,11 @@ def llama_plan(cfg: LlamaConfig) -> ModelPlan:
 
 
 register_architecture("LlamaForCausalLM", LlamaConfig.from_dict, llama_plan)
+
+
+def _register_fomatar():
+    from .fomatar import FomatarConfig, fomatar_plan
+    register_architecture("Fomatar", FomatarConfig.from_dict, fomatar_plan)
+
+
+_register_fomatar()

@@ -33,6 +33,9 @@ MODULES = {
     "sampling": ["sampling.cu", "decode_loop.cu"],
     "gemm_tc": ["gemm_tc.cu"],
     "random_fill": ["random_fill.cu"],
+    "token_ops": ["token_ops.cu"],
+    "recurrence": ["recurrence.cu"],
+    "attention_window": ["attention_window.cu"],
 }
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]

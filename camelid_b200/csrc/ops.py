@@ -75,6 +75,34 @@ _SIGNATURES = {
     ("sampling", "cml_draws_at"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     ("sampling", "cml_sample_rows"): [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p],
+    ("token_ops", "cml_bigram_embed"): [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, ctypes.c_longlong, ctypes.c_longlong,
+                                        ctypes.c_longlong, c_void_p, c_void_p],
+    ("token_ops", "cml_keep_last_rows"): [c_void_p, c_int, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_int, c_void_p],
+    ("token_ops", "cml_token_shift"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_int, c_int, c_void_p],
+    ("token_ops", "cml_add_rows_vec"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    ("token_ops", "cml_gelu_tanh"): [c_void_p, c_int, c_long, c_void_p],
+    ("token_ops", "cml_softcap"): [c_void_p, c_long, c_float, c_void_p],
+    ("token_ops", "cml_norm_combine"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_float,
+                                        c_float, c_void_p],
+    ("recurrence", "cml_conv_unit"): [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    ("recurrence", "cml_delta_scan"): [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_long, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                       c_int, c_void_p],
+    ("recurrence", "cml_memory_scan"): [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                                        c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                        c_int, c_int, c_void_p],
+    ("recurrence", "cml_head_norm_gate"): [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_long, c_int, c_void_p, c_int,
+                                           c_int, c_int, c_int, c_float, c_void_p],
+    ("attention_window", "cml_qk_norm_kv_write"): [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p,
+                                                   c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                   c_int, c_int, c_int, c_int, c_void_p],
+    ("attention_window", "cml_window_attention"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                                   c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int,
+                                                   c_int, c_int, c_int, c_float, c_void_p],
     ("random_fill", "cml_random_fill"): [c_void_p, c_int, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_ulonglong,
                                          ctypes.c_double, ctypes.c_double, c_void_p],
 }
@@ -274,6 +302,206 @@ def rope_kv_from_partials(partial: torch.Tensor, q_out: torch.Tensor, row_pos, r
         _p(row_pos), _p(row_seq), _p(block_table), block_table.shape[1] if write_kv else 0, _p(k_pages), _p(v_pages),
         _p(inv_freq), rotary_dim, n_heads, n_kv_heads, head_dim, 1 if write_kv else 0, _stream()),
         "rope_kv_from_partials")
+
+
+# ---------------------------------------------------------------------------------------
+# what a sequence carries from token to token besides keys and values, and small row-wise steps
+
+def bigram_embed(table: torch.Tensor, bigram, tokens, row_seq, row_pos, seq_row0, seq_new, seq_slot, prev_state, out,
+                 n_seqs: int, buckets: int, mul_prev: int, mul_cur: int, err: torch.Tensor):
+    """out[r] = table[tokens[r]] (+ bigram[hash of the previous and this token], the last row for a
+    sequence's first token) as float32; ``prev_state`` (int32 [slots]) gives the token before a
+    step's first row and takes the step's last token."""
+    _dev(table, bigram, tokens, row_seq, row_pos, seq_row0, seq_new, seq_slot, prev_state, out, err)
+    rows, hidden = out.shape
+    assert table.shape[1] == hidden and tokens.dtype == torch.int32 and out.dtype == torch.float32
+    assert table.is_contiguous() and out.is_contiguous()
+    if bigram is not None:
+        assert bigram.dtype == table.dtype and bigram.shape == (buckets + 1, hidden) and bigram.is_contiguous()
+        assert prev_state.dtype == torch.int32 and prev_state.is_contiguous()
+    _check(_fn("token_ops", "cml_bigram_embed")(_p(table), _p(bigram), dtype_code(table.dtype), _p(tokens), _p(row_seq),
+                                                _p(row_pos), _p(seq_row0), _p(seq_new), _p(seq_slot), _p(prev_state), _p(out),
+                                                rows, n_seqs, hidden, table.shape[0], int(buckets or 1), int(mul_prev or 0),
+                                                int(mul_cur or 0), _p(err), _stream()),
+           "bigram_embed", 2 if bigram is not None else 1)
+
+
+def keep_last_rows(src: torch.Tensor, col0: int, width: int, state: torch.Tensor, seq_row0, seq_new, seq_start, seq_slot,
+                   n_seqs: int):
+    """state[slot] (float32 [slots, keep, width]) = columns col0.. of each sequence's last ``keep`` rows
+    after this step (rows of ``src`` where the step brought them, else what the state held)."""
+    _dev(src, state, seq_row0, seq_new, seq_start, seq_slot)
+    assert src.dim() == 2 and src.stride(1) == 1 and col0 + width <= src.shape[1]
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 3 and state.shape[2] == width
+    _check(_fn("token_ops", "cml_keep_last_rows")(_p(src), dtype_code(src.dtype), src.stride(0), col0, width, state.shape[1],
+                                                  _p(seq_row0), _p(seq_new), _p(seq_start), _p(seq_slot), _p(state), n_seqs,
+                                                  _stream()), "keep_last_rows")
+
+
+def token_shift(h: torch.Tensor, mix: torch.Tensor, state: torch.Tensor, row_seq, row_pos, seq_row0, seq_slot,
+                out: torch.Tensor):
+    """out[r] = h[r] + (h[r - 1] - h[r]) * mix within a sequence; zeros before the first token,
+    ``state[slot]`` (float32 [slots, hidden]) before a step's first row."""
+    _dev(h, mix, state, row_seq, row_pos, seq_row0, seq_slot, out)
+    rows, hidden = h.shape
+    assert h.is_contiguous() and out.is_contiguous() and out.shape == h.shape and out.dtype == h.dtype
+    assert mix.numel() == hidden and state.dtype == torch.float32 and state.shape[-1] == hidden and state.is_contiguous()
+    _check(_fn("token_ops", "cml_token_shift")(_p(h), dtype_code(h.dtype), _p(mix), dtype_code(mix.dtype), _p(state),
+                                               _p(row_seq), _p(row_pos), _p(seq_row0), _p(seq_slot), _p(out), rows, hidden,
+                                               _stream()), "token_shift")
+
+
+def add_rows_vec(h: torch.Tensor, base, vec: torch.Tensor):
+    """h[r] += (base[r] if given) + vec, float32 rows in place."""
+    _dev(h, base, vec)
+    rows, hidden = h.shape
+    assert h.dtype == torch.float32 and h.is_contiguous() and vec.numel() == hidden and vec.is_contiguous()
+    if base is not None:
+        assert base.dtype == torch.float32 and base.shape == h.shape and base.is_contiguous()
+    _check(_fn("token_ops", "cml_add_rows_vec")(_p(h), _p(base), _p(vec), dtype_code(vec.dtype), rows, hidden, _stream()),
+           "add_rows_vec")
+
+
+def gelu_tanh_(x: torch.Tensor):
+    """x = 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))) in place."""
+    _dev(x)
+    assert x.is_contiguous()
+    _check(_fn("token_ops", "cml_gelu_tanh")(_p(x), dtype_code(x.dtype), x.numel(), _stream()), "gelu_tanh")
+
+
+def softcap_(x: torch.Tensor, cap: float):
+    """x = cap * tanh(x / cap) in place (float32)."""
+    _dev(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(_fn("token_ops", "cml_softcap")(_p(x), x.numel(), float(cap), _stream()), "softcap")
+
+
+def norm_combine(branches: list, residual: torch.Tensor, eps: float, coef: float):
+    """residual[r] += coef * sum of rmsnorm(y[r]) * w over ``branches`` = [(y, w)], y float32
+    [rows, hidden] or [splits, rows, hidden] (splits summed first), w [hidden]."""
+    rows, hidden = residual.shape
+    assert 1 <= len(branches) <= 4 and residual.dtype == torch.float32 and residual.is_contiguous()
+    n = len(branches)
+    ys, ws, splits, strides = (c_void_p * n)(), (c_void_p * n)(), (c_int * n)(), (c_long * n)()
+    for i, (y, w) in enumerate(branches):
+        _dev(y, w)
+        if y.dim() == 2:
+            y = y.unsqueeze(0)
+        assert y.dtype == torch.float32 and y.shape[1:] == (rows, hidden) and y.stride(2) == 1 and y.stride(1) == hidden
+        assert w.numel() == hidden and w.is_contiguous() and w.dtype == branches[0][1].dtype
+        ys[i], ws[i], splits[i], strides[i] = y.data_ptr(), w.data_ptr(), y.shape[0], y.stride(0)
+    _check(_fn("token_ops", "cml_norm_combine")(ys, ws, splits, strides, n, dtype_code(branches[0][1].dtype), _p(residual),
+                                                rows, hidden, float(eps), float(coef), _stream()), "norm_combine")
+
+
+# ---------------------------------------------------------------------------------------
+# recurrent mixers with a matrix state per head
+
+def conv_unit(proj: torch.Tensor, conv_w: torch.Tensor, state: torch.Tensor, row_seq, row_pos, seq_row0, seq_slot,
+              out: torch.Tensor, qk_heads: int, heads: int, key_dim: int, value_dim: int, q_scale: float):
+    """Short causal convolution + SiLU over the q, k, v channels at the start of ``proj``'s columns
+    (float32), then unit norm of q and k per head, q times ``q_scale``. ``conv_w`` float32
+    [channels, taps]; ``state`` float32 [slots, taps - 1, channels]: the inputs before the step."""
+    _dev(proj, conv_w, state, row_seq, row_pos, seq_row0, seq_slot, out)
+    channels, taps = conv_w.shape
+    rows = out.shape[0]
+    assert channels == 2 * qk_heads * key_dim + heads * value_dim and proj.shape[1] >= channels
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and conv_w.dtype == torch.float32 and conv_w.is_contiguous()
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (rows, channels)
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (max(taps - 1, 1), channels)
+    _check(_fn("recurrence", "cml_conv_unit")(_p(proj), proj.stride(0), _p(conv_w), _p(state), _p(row_seq), _p(row_pos),
+                                              _p(seq_row0), _p(seq_slot), _p(out), rows, qk_heads, heads, key_dim, value_dim,
+                                              taps, float(q_scale), _stream()), "conv_unit")
+
+
+def delta_scan(qkv: torch.Tensor, beta_in: torch.Tensor, beta_col: int, decay_in: torch.Tensor, a_log, dt_bias,
+               state: torch.Tensor, seq_row0, seq_new, seq_start, seq_slot, out: torch.Tensor, n_seqs: int, heads: int,
+               qk_heads: int, key_dim: int, value_dim: int):
+    """The gated delta rule over each sequence's new rows; ``state`` float32 [slots, heads, key_dim,
+    value_dim] is read and replaced; ``out`` float32 [rows, heads * value_dim] = S^T q."""
+    _dev(qkv, beta_in, decay_in, a_log, dt_bias, state, seq_row0, seq_new, seq_start, seq_slot, out)
+    for t in (qkv, beta_in, decay_in, out, state, a_log, dt_bias):
+        assert t.dtype == torch.float32 and t.stride(-1) == 1
+    assert state.is_contiguous() and state.shape[1:] == (heads, key_dim, value_dim) and out.is_contiguous()
+    assert decay_in.shape[1] == heads * key_dim and out.shape[1] == heads * value_dim
+    _check(_fn("recurrence", "cml_delta_scan")(_p(qkv), qkv.stride(0), _p(beta_in), beta_in.stride(0), beta_col, _p(decay_in),
+                                               decay_in.stride(0), _p(a_log), _p(dt_bias), _p(state), _p(seq_row0),
+                                               _p(seq_new), _p(seq_start), _p(seq_slot), _p(out), n_seqs, heads, qk_heads,
+                                               key_dim, value_dim, _stream()), "delta_scan")
+
+
+def memory_scan(proj: torch.Tensor, cols: tuple, i_bias, f_bias, cap: float, q_scale: float, state: torch.Tensor, seq_row0,
+                seq_new, seq_start, seq_slot, out: torch.Tensor, n_seqs: int, heads: int, key_dim: int, value_dim: int):
+    """The matrix memory with exponential gates over each sequence's new rows. ``cols``: columns of
+    q, k, v, input gate, forget gate in ``proj`` (float32). ``state`` float32 [slots, heads,
+    key_dim + 1, value_dim + 1]; ``out`` float32 [rows, heads, value_dim + 2]."""
+    _dev(proj, i_bias, f_bias, state, seq_row0, seq_new, seq_start, seq_slot, out)
+    for t in (proj, i_bias, f_bias, state, out):
+        assert t.dtype == torch.float32 and t.stride(-1) == 1
+    assert state.is_contiguous() and state.shape[1:] == (heads, key_dim + 1, value_dim + 1)
+    assert out.is_contiguous() and out.shape[1:] == (heads, value_dim + 2)
+    q_col, k_col, v_col, i_col, f_col = cols
+    _check(_fn("recurrence", "cml_memory_scan")(_p(proj), proj.stride(0), q_col, k_col, v_col, i_col, f_col, _p(i_bias),
+                                                _p(f_bias), float(cap), float(q_scale), _p(state), _p(seq_row0), _p(seq_new),
+                                                _p(seq_start), _p(seq_slot), _p(out), n_seqs, heads, key_dim, value_dim,
+                                                _stream()), "memory_scan")
+
+
+def head_norm_gate(raw: torch.Tensor, with_den: bool, w: torch.Tensor, w_per_head: bool, gate: torch.Tensor, gate_col: int,
+                   out: torch.Tensor, heads: int, value_dim: int, eps: float):
+    """Per (row, head): the scan's output (divided by its denominator where it carries one), RMS
+    norm over value_dim, times ``w`` (float32 [value_dim] or [heads * value_dim]) and
+    sigmoid(gate[:, gate_col + ...]); ``out`` [rows, heads * value_dim] in the compute type."""
+    _dev(raw, w, gate, out)
+    rows = out.shape[0]
+    ldh = value_dim + 2 if with_den else value_dim
+    assert raw.dtype == torch.float32 and raw.is_contiguous() and raw.numel() == rows * heads * ldh
+    assert w.dtype == torch.float32 and w.numel() == (heads * value_dim if w_per_head else value_dim)
+    assert gate.dtype == torch.float32 and gate.stride(1) == 1 and out.is_contiguous() and out.shape[1] == heads * value_dim
+    _check(_fn("recurrence", "cml_head_norm_gate")(_p(raw), ldh, 1 if with_den else 0, _p(w), value_dim if w_per_head else 0,
+                                                   _p(gate), gate.stride(0), gate_col, _p(out), dtype_code(out.dtype), rows,
+                                                   heads, value_dim, float(eps), _stream()), "head_norm_gate")
+
+
+# ---------------------------------------------------------------------------------------
+# windowed attention with keys and values of different sizes
+
+def qk_norm_kv_write(proj: torch.Tensor, q_w, k_w, eps: float, row_seq, row_pos, table, q_out, k_pages, v_pages,
+                     heads: int, kv_heads: int, key_dim: int, value_dim: int):
+    """From ``proj`` (float32 rows: q, k, v): q and k RMS-normed per head with the weights ``q_w``,
+    ``k_w`` (None: as they are); q to ``q_out``, k and v into their pages, all in the compute type."""
+    _dev(proj, q_w, k_w, row_seq, row_pos, table, q_out, k_pages, v_pages)
+    rows = q_out.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1
+    assert proj.shape[1] >= heads * key_dim + kv_heads * (key_dim + value_dim)
+    assert q_out.is_contiguous() and q_out.shape[1] == heads * key_dim and k_pages.dtype == q_out.dtype == v_pages.dtype
+    assert k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert k_pages.shape[1:] == (kv_heads, PAGE, key_dim) and v_pages.shape[1:] == (kv_heads, PAGE, value_dim)
+    norm = q_w is not None
+    if norm:
+        assert q_w.numel() == key_dim and k_w.numel() == key_dim and q_w.dtype == k_w.dtype
+    _check(_fn("attention_window", "cml_qk_norm_kv_write")(
+        _p(proj), proj.stride(0), _p(q_w), _p(k_w), dtype_code(q_w.dtype) if norm else dtype_code(q_out.dtype), 1 if norm else 0,
+        float(eps), _p(row_seq), _p(row_pos), _p(table), table.shape[1], _p(q_out), _p(k_pages), _p(v_pages),
+        dtype_code(q_out.dtype), rows, heads, kv_heads, key_dim, value_dim, _stream()), "qk_norm_kv_write")
+
+
+def window_attention(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate, gate_col: int, out, heads: int,
+                     kv_heads: int, key_dim: int, value_dim: int, window: int, scale: float):
+    """out[r, head] = softmax_j((q . k_j) scale - r1 ln(1 + r2 (i - j))) V over the last ``window`` keys
+    (0: all), times sigmoid(gate[r, gate_col + ...]) where ``gate`` (float32) is given."""
+    _dev(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate, out)
+    rows = q.shape[0]
+    assert q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype == k_pages.dtype == v_pages.dtype
+    assert out.shape == (rows, heads * value_dim) and q.shape[1] == heads * key_dim
+    if r1 is not None:
+        assert r1.dtype == torch.float32 and r2.dtype == torch.float32 and r1.numel() == heads and r2.numel() == heads
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1
+    _check(_fn("attention_window", "cml_window_attention")(
+        _p(q), _p(k_pages), _p(v_pages), dtype_code(q.dtype), _p(table), table.shape[1], _p(row_seq), _p(row_pos), _p(r1),
+        _p(r2), _p(gate), gate.stride(0) if gate is not None else 0, gate_col, _p(out), rows, heads, kv_heads, key_dim,
+        value_dim, int(window or 0), float(scale), _stream()), "window_attention")
 
 
 TC_STORE, TC_STORE_F32, TC_ADD_F32, TC_SWIGLU, TC_T_PARTIAL, TC_T_SWIGLU = 0, 1, 2, 3, 4, 5

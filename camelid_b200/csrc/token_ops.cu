@@ -1,0 +1,296 @@
+// Kernels for what a sequence carries from token to token besides keys and values: the
+// previous token of a hashed bigram embedding, the previous rows of a token shift or a short
+// convolution; and the small row-wise steps of decoders that need them: the input of a pass
+// over a looped stretch of layers, GELU, the soft cap of logits, the mean of several normed
+// branch outputs.
+//
+// A step's rows are packed: sequence s owns rows seq_row0[s] .. + seq_new[s]; row r belongs to
+// row_seq[r] and stands at position row_pos[r]; the state of sequence s lies at seq_slot[s].
+// A kernel that reads state and one that replaces it are separate launches, so a step of many
+// rows never reads what it has just written. All arithmetic in float.
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------
+// out[r] = table[tok] + bigram[(prev * mul_prev + tok * mul_cur) mod buckets]; the row
+// `buckets` for a sequence's first token. prev is the token of the row before, or, for the
+// first row of a step, what `prev_state[slot]` kept. bigram may be null (plain embedding).
+template <typename T>
+__global__ void bigram_embed_kernel(const T* __restrict__ table, const T* __restrict__ bigram, const int* __restrict__ tokens,
+                                    const int* __restrict__ row_seq, const int* __restrict__ row_pos,
+                                    const int* __restrict__ seq_row0, const int* __restrict__ seq_slot,
+                                    const int* __restrict__ prev_state, float* __restrict__ out, int hidden, int vocab,
+                                    long long buckets, long long mul_prev, long long mul_cur, int* err) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const int tok = tokens[r];
+    float* o = out + (size_t)r * hidden;
+    if (tok < 0 || tok >= vocab) {
+        if (threadIdx.x == 0) atomicOr(err, 1);
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = 0.f;
+        return;
+    }
+    const T* src = table + (size_t)tok * hidden;
+    if (!bigram) {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = to_f32(src[c]);
+        return;
+    }
+    const int s = row_seq[r];
+    long long brow = buckets;
+    if (row_pos[r] > 0) {
+        const int prev = r > seq_row0[s] ? tokens[r - 1] : prev_state[seq_slot[s]];
+        brow = ((long long)prev * mul_prev + (long long)tok * mul_cur) % buckets;
+        if (brow < 0) brow += buckets;
+    }
+    const T* b = bigram + (size_t)brow * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = to_f32(src[c]) + to_f32(b[c]);
+}
+
+// prev_state[slot of s] = the last token sequence s brought in this step.
+__global__ void keep_last_token_kernel(const int* __restrict__ tokens, const int* __restrict__ seq_row0,
+                                       const int* __restrict__ seq_new, const int* __restrict__ seq_slot,
+                                       int* __restrict__ prev_state, int n_seqs) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s < n_seqs) prev_state[seq_slot[s]] = tokens[seq_row0[s] + seq_new[s] - 1];
+}
+
+extern "C" int cml_bigram_embed(const void* table, const void* bigram, int dtype, const int* tokens, const int* row_seq,
+                                const int* row_pos, const int* seq_row0, const int* seq_new, const int* seq_slot,
+                                int* prev_state, float* out, int rows, int n_seqs, int hidden, int vocab, long long buckets,
+                                long long mul_prev, long long mul_cur, int* err, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int block = hidden >= 1024 ? 256 : 128;
+    if (dtype == CML_DTYPE_F32)
+        launch_pdl(bigram_embed_kernel<float>, dim3(rows), dim3(block), 0, s, (const float*)table, (const float*)bigram, tokens,
+                   row_seq, row_pos, seq_row0, seq_slot, (const int*)prev_state, out, hidden, vocab, buckets, mul_prev, mul_cur, err);
+    else if (dtype == CML_DTYPE_BF16)
+        launch_pdl(bigram_embed_kernel<bf16>, dim3(rows), dim3(block), 0, s, (const bf16*)table, (const bf16*)bigram, tokens,
+                   row_seq, row_pos, seq_row0, seq_slot, (const int*)prev_state, out, hidden, vocab, buckets, mul_prev, mul_cur, err);
+    else
+        return CML_ERR_BAD_DTYPE;
+    if (bigram)
+        launch_pdl(keep_last_token_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, s, tokens, seq_row0, seq_new, seq_slot,
+                   prev_state, n_seqs);
+    return cml_launch_status();
+}
+
+// ------------------------------------------------------------------------------------
+// state[slot, j, c] (j < keep) = the value of column col0 + c of the sequence's (keep - j)-th
+// last row after this step: a row of this step where it brought that many, else what the state
+// held (zeros for a sequence that starts here). A thread owns one column of one sequence.
+template <typename T>
+__global__ void keep_last_rows_kernel(const T* __restrict__ src, long ld, int col0, int width, int keep,
+                                      const int* __restrict__ seq_row0, const int* __restrict__ seq_new,
+                                      const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                                      float* __restrict__ state) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int s = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    const int n = seq_new[s], row0 = seq_row0[s];
+    const bool fresh = seq_start[s] == 0;
+    float* st = state + (size_t)seq_slot[s] * keep * width + c;
+    for (int j = 0; j < keep; ++j) {
+        const int o = n - keep + j;                       // offset of that row among the step's rows
+        float v;
+        if (o >= 0) v = to_f32(src[(size_t)(row0 + o) * ld + col0 + c]);
+        else v = fresh ? 0.f : st[(size_t)(n + j) * width];
+        st[(size_t)j * width] = v;
+    }
+}
+
+extern "C" int cml_keep_last_rows(const void* src, int dtype, long ld, int col0, int width, int keep, const int* seq_row0,
+                                  const int* seq_new, const int* seq_start, const int* seq_slot, float* state, int n_seqs,
+                                  void* stream) {
+    if (n_seqs <= 0 || width <= 0 || keep <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid((width + 127) / 128, n_seqs);
+    if (dtype == CML_DTYPE_F32)
+        launch_pdl(keep_last_rows_kernel<float>, grid, dim3(128), 0, s, (const float*)src, ld, col0, width, keep, seq_row0, seq_new,
+                   seq_start, seq_slot, state);
+    else if (dtype == CML_DTYPE_BF16)
+        launch_pdl(keep_last_rows_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)src, ld, col0, width, keep, seq_row0, seq_new,
+                   seq_start, seq_slot, state);
+    else
+        return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}
+
+// ------------------------------------------------------------------------------------
+// Token shift: out[r] = h[r] + (h'[r] - h[r]) * mix, h' the row before of the same sequence
+// (zeros for the first token; state[slot] for the first row of a later step).
+template <typename T, typename TW>
+__global__ void token_shift_kernel(const T* __restrict__ h, const TW* __restrict__ mix, const float* __restrict__ state,
+                                   const int* __restrict__ row_seq, const int* __restrict__ row_pos,
+                                   const int* __restrict__ seq_row0, const int* __restrict__ seq_slot, T* __restrict__ out,
+                                   int hidden) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const int s = row_seq[r];
+    const bool first = row_pos[r] == 0, inside = r > seq_row0[s];
+    const T* cur = h + (size_t)r * hidden;
+    const T* before = h + (size_t)(inside ? r - 1 : r) * hidden;
+    const float* st = state + (size_t)seq_slot[s] * hidden;
+    T* o = out + (size_t)r * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float x = to_f32(cur[c]);
+        const float p = first ? 0.f : (inside ? to_f32(before[c]) : st[c]);
+        o[c] = from_f32<T>(x + (p - x) * to_f32(mix[c]));
+    }
+}
+
+extern "C" int cml_token_shift(const void* h, int dtype, const void* mix, int mix_dtype, const float* state, const int* row_seq,
+                               const int* row_pos, const int* seq_row0, const int* seq_slot, void* out, int rows, int hidden,
+                               void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int block = hidden >= 1024 ? 256 : 128;
+#define TS_CASE(T_, TW_, D_, DW_)                                                                                         \
+    if (dtype == D_ && mix_dtype == DW_) {                                                                                \
+        launch_pdl(token_shift_kernel<T_, TW_>, dim3(rows), dim3(block), 0, s, (const T_*)h, (const TW_*)mix, state, row_seq, \
+                   row_pos, seq_row0, seq_slot, (T_*)out, hidden);                                                         \
+        return cml_launch_status();                                                                                       \
+    }
+    TS_CASE(float, float, CML_DTYPE_F32, CML_DTYPE_F32)
+    TS_CASE(bf16, bf16, CML_DTYPE_BF16, CML_DTYPE_BF16)
+    TS_CASE(bf16, float, CML_DTYPE_BF16, CML_DTYPE_F32)
+    TS_CASE(float, bf16, CML_DTYPE_F32, CML_DTYPE_BF16)
+#undef TS_CASE
+    return CML_ERR_BAD_DTYPE;
+}
+
+// ------------------------------------------------------------------------------------
+// h[r] += (base ? base[r] : 0) + vec: the input of one pass over a looped stretch.
+template <typename TW>
+__global__ void add_rows_vec_kernel(float* __restrict__ h, const float* __restrict__ base, const TW* __restrict__ vec,
+                                    long n, int hidden) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        float v = h[i];
+        if (base) v += base[i];
+        h[i] = v + to_f32(vec[i % hidden]);
+    }
+}
+
+extern "C" int cml_add_rows_vec(float* h, const float* base, const void* vec, int vec_dtype, int rows, int hidden, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long n = (long)rows * hidden;
+    const int grid = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    if (vec_dtype == CML_DTYPE_F32)
+        launch_pdl(add_rows_vec_kernel<float>, dim3(grid), dim3(256), 0, s, h, base, (const float*)vec, n, hidden);
+    else if (vec_dtype == CML_DTYPE_BF16)
+        launch_pdl(add_rows_vec_kernel<bf16>, dim3(grid), dim3(256), 0, s, h, base, (const bf16*)vec, n, hidden);
+    else
+        return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}
+
+// ------------------------------------------------------------------------------------
+// x = 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))) in place.
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+template <typename T>
+__global__ void gelu_tanh_kernel(T* __restrict__ x, long n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+        x[i] = from_f32<T>(gelu_tanh_f(to_f32(x[i])));
+}
+
+extern "C" int cml_gelu_tanh(void* x, int dtype, long n, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int grid = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+    if (dtype == CML_DTYPE_F32) launch_pdl(gelu_tanh_kernel<float>, dim3(grid), dim3(256), 0, s, (float*)x, n);
+    else if (dtype == CML_DTYPE_BF16) launch_pdl(gelu_tanh_kernel<bf16>, dim3(grid), dim3(256), 0, s, (bf16*)x, n);
+    else return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}
+
+// x = cap * tanh(x / cap) in place (float logits).
+__global__ void softcap_kernel(float* __restrict__ x, long n, float cap) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] / cap);
+}
+
+extern "C" int cml_softcap(float* x, long n, float cap, void* stream) {
+    if (n <= 0) return 0;
+    const int grid = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+    launch_pdl(softcap_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, x, n, cap);
+    return cml_launch_status();
+}
+
+// ------------------------------------------------------------------------------------
+// residual[r] += coef * sum over branches b of rmsnorm(y_b[r]) * w_b. Each y_b is a float
+// matrix [splits_b, rows, hidden] whose splits are summed first, in index order. One block
+// per row; the row of each branch is kept in shared memory between the two passes.
+struct CombineBranches {
+    const float* y[4];
+    const void* w[4];
+    int splits[4];
+    long split_stride[4];
+    int n;
+};
+
+template <typename TW>
+__global__ void norm_combine_kernel(CombineBranches br, float* __restrict__ residual, int hidden, float eps, float coef) {
+    __shared__ float red[33];
+    extern __shared__ float rowbuf[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    float* res = residual + (size_t)r * hidden;
+    for (int b = 0; b < br.n; ++b) {
+        const float* y = br.y[b] + (size_t)r * hidden;
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            float v = y[c];
+            for (int s = 1; s < br.splits[b]; ++s) v += y[(size_t)s * br.split_stride[b] + c];
+            rowbuf[c] = v;
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, red);
+        const float scale = coef / sqrtf(ss / (float)hidden + eps);
+        const TW* w = (const TW*)br.w[b];
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) res[c] += rowbuf[c] * scale * to_f32(w[c]);
+        __syncthreads();
+    }
+}
+
+extern "C" int cml_norm_combine(const float* const* y, const void* const* w, const int* splits, const long* split_stride,
+                                int n_branches, int w_dtype, float* residual, int rows, int hidden, float eps, float coef,
+                                void* stream) {
+    if (rows <= 0) return 0;
+    if (n_branches < 1 || n_branches > 4) return CML_ERR_BAD_SIZE;
+    CombineBranches br;
+    br.n = n_branches;
+    for (int b = 0; b < 4; ++b) {
+        br.y[b] = b < n_branches ? y[b] : nullptr;
+        br.w[b] = b < n_branches ? w[b] : nullptr;
+        br.splits[b] = b < n_branches ? splits[b] : 0;
+        br.split_stride[b] = b < n_branches ? split_stride[b] : 0;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const int block = hidden >= 1024 ? 256 : 128;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
+    if (w_dtype == CML_DTYPE_F32) {
+        if (smem > 48 * 1024 && cml_allow_smem<norm_combine_kernel<float>>(smem) != cudaSuccess) return CML_ERR_BAD_SIZE;
+        launch_pdl(norm_combine_kernel<float>, dim3(rows), dim3(block), smem, s, br, residual, hidden, eps, coef);
+    } else if (w_dtype == CML_DTYPE_BF16) {
+        if (smem > 48 * 1024 && cml_allow_smem<norm_combine_kernel<bf16>>(smem) != cudaSuccess) return CML_ERR_BAD_SIZE;
+        launch_pdl(norm_combine_kernel<bf16>, dim3(rows), dim3(block), smem, s, br, residual, hidden, eps, coef);
+    } else
+        return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}

@@ -212,9 +212,10 @@ class StepContext:
         entry = self.cache_source if self.cache_source is not None else self.entry
         return self.cache.kv_pages(entry)
 
-    def state(self) -> torch.Tensor:
-        """[slots, *shape] fixed-size state of the running entry; index it with ``seq_slot``."""
-        return self.cache.state_of(self.entry)
+    def state(self, name: str | None = None) -> torch.Tensor:
+        """[slots, *shape] fixed-size state of the running entry (``name`` picks one where the entry
+        keeps several); index it with ``seq_slot``."""
+        return self.cache.state_of(self.entry, name)
 
     def query_tiles(self, rows_per_tile: int):
         """Tiles of at most ``rows_per_tile`` consecutive new rows of one sequence:

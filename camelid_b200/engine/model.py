@@ -65,6 +65,7 @@ class DecoderModel:
         self.blocks = [build_block(layer) for layer in plan.layers]
         self.final_norm = build_part("norm", plan.final_norm)
         self.head = build_part("head", plan.head)
+        self.pass_input = build_part("pass_input", plan.pass_input) if plan.pass_input is not None else None
         self.schedule = list(plan.schedule)
         self.hidden_size = plan.hidden_size
         self.vocab_size = plan.vocab_size
@@ -72,16 +73,17 @@ class DecoderModel:
         self.workspace = Workspace(self.device)
         self._err = None
         self._logit_err = None
+        self.layer_probe = None         # debugging: called with (schedule entry, settled residual stream) after every layer run
         self.last_h2d_bytes = 0
         self.tile_sizes = sorted({r for b in self.blocks for r in b.query_tile_sizes()}) or [1]
         # decode steps replay captured CUDA graphs when every part can run inside one
         self.use_graphs = all(b.graph_safe for b in self.blocks) and all(
-            p.graph_safe for p in (self.embedding, self.final_norm, self.head))
+            p.graph_safe for p in self._single_parts())
         self._graphs = weakref.WeakKeyDictionary()      # cache -> {(sequences, widths, feed): DecodeGraph}
         # steps of several tokens per sequence: layouts seen once, and the graphs of those seen again
         self.capture_steps = (self.use_graphs and self.options.capture_repeated_steps
                               and all(b.graph_safe_any_step for b in self.blocks)
-                              and all(p.graph_safe_any_step for p in (self.embedding, self.final_norm, self.head)))
+                              and all(p.graph_safe_any_step for p in self._single_parts()))
         self._seen_layouts = weakref.WeakKeyDictionary()   # cache -> {key: times seen}
         self._step_graphs = weakref.WeakKeyDictionary()    # cache -> {key: StepGraph}, oldest first
 
@@ -102,8 +104,14 @@ class DecoderModel:
             files.close()
         return model
 
+    def _single_parts(self) -> list:
+        """The parts that are not layers."""
+        return [p for p in (self.embedding, self.final_norm, self.head, self.pass_input) if p is not None]
+
     def tensor_specs(self) -> dict:
         specs = dict(self.embedding.tensor_specs())
+        if self.pass_input is not None:
+            specs.update(self.pass_input.tensor_specs())
         for b in self.blocks:
             specs.update(b.tensor_specs())
         specs.update(self.final_norm.tensor_specs())
@@ -138,6 +146,8 @@ class DecoderModel:
                 return get(name)
         tensors = _Lazy()
         self.embedding.load(tensors, self.device, self.dtype)
+        if self.pass_input is not None:
+            self.pass_input.load(tensors, self.device, self.dtype)
         for b in self.blocks:
             b.load(tensors, self.device, self.dtype)
         self.final_norm.load(tensors, self.device, self.dtype)
@@ -149,7 +159,12 @@ class DecoderModel:
 
     # ---- cache ----
     def entry_cache_specs(self) -> list:
-        return [self.blocks[e.layer].cache_spec() for e in self.schedule]
+        """What each schedule entry asks of the cache; one more entry at the end for what the
+        embedding keeps per sequence (the previous token of a bigram embedding)."""
+        return [self.blocks[e.layer].cache_spec() for e in self.schedule] + [self.embedding.cache_spec()]
+
+    def entry_cache_sources(self) -> list:
+        return [e.cache_source for e in self.schedule] + [None]
 
     def new_cache(self, max_tokens: int, max_slots: int | None = None) -> SequenceCache:
         """A cache for at most ``max_tokens`` live tokens (each sequence's count rounded up to
@@ -159,7 +174,7 @@ class DecoderModel:
         if free is not None:
             self.memory_plan(max_tokens, max_slots).check(free, f"a cache for {max_tokens} tokens on {self.device}",
                                                           parts=("cache", "workspace"))
-        return SequenceCache(self.entry_cache_specs(), [e.cache_source for e in self.schedule],
+        return SequenceCache(self.entry_cache_specs(), self.entry_cache_sources(),
                              max_tokens=max_tokens, max_position=self.plan.max_position, dtype=self.dtype,
                              device=self.device, max_slots=max_slots)
 
@@ -374,11 +389,23 @@ class DecoderModel:
         ctx.deferred = None
         ctx.row_scale = None
         h = ctx.buffer("hidden", (ctx.n_rows, self.hidden_size), torch.float32)
+        ctx.entry = len(self.schedule)                      # the embedding's own entry of the cache
+        ctx.cache_source = None
         self.embedding.forward(ctx, ctx.tokens, h, self._err)
+        base = None
+        if self.pass_input is not None and getattr(self.pass_input, "needs_base", False):
+            base = ctx.buffer("embedding_output", (ctx.n_rows, self.hidden_size), torch.float32)
+            base.copy_(h)
         for i, e in enumerate(self.schedule):
             ctx.entry = i
             ctx.cache_source = e.cache_source
+            if e.pass_number is not None:                   # the first layer of a pass over a looped stretch
+                ctx.settle(h)
+                self.pass_input.forward(ctx, h, base, e.pass_number)
             self.blocks[e.layer].forward(ctx, h)
+            if self.layer_probe is not None:
+                ctx.settle(h)
+                self.layer_probe(i, h)
         logits = torch.empty((ctx.n_want, self.vocab_size), dtype=torch.float32, device=self.device)
         if ctx.n_want:
             if not self.final_norm.handles_pending:          # a norm from outside reads a settled stream

@@ -17,7 +17,7 @@ from dataclasses import dataclass
 
 import torch
 
-from .cache.book import PAGE, KVSpec, StateSpec
+from .cache.book import PAGE, KVSpec, StateSpec, flatten_specs
 from .errors import CacheError
 
 
@@ -72,17 +72,18 @@ def plan_for_model(model, max_tokens: int = 0, max_slots: int | None = None, ste
     n_pages = max(1, (int(max_tokens) + PAGE - 1) // PAGE) if max_tokens else 0
     n_slots = int(max_slots) if max_slots else n_pages
     cache = 0
-    seen_sources = [src for src in (entry.cache_source for entry in model.schedule)]
+    seen_sources = model.entry_cache_sources()
     widest_kv = 0
-    for spec, src in zip(model.entry_cache_specs(), seen_sources):
-        if src is not None or spec is None:
+    for entry_needs, src in zip(model.entry_cache_specs(), seen_sources):
+        if src is not None:
             continue
-        if isinstance(spec, KVSpec):
-            cache += 2 * n_pages * spec.n_kv_heads * PAGE * spec.head_dim * e
-            widest_kv = max(widest_kv, spec.n_kv_heads * spec.head_dim)
-        elif isinstance(spec, StateSpec):
-            from .cache.sequence_cache import _STATE_DTYPES
-            cache += n_slots * _numel(spec.shape) * _elem(_STATE_DTYPES[spec.dtype])
+        for spec in flatten_specs(entry_needs):
+            if isinstance(spec, KVSpec):
+                cache += n_pages * spec.n_kv_heads * PAGE * (spec.head_dim + spec.value_dim) * e
+                widest_kv = max(widest_kv, spec.n_kv_heads * max(spec.head_dim, spec.value_dim))
+            elif isinstance(spec, StateSpec):
+                from .cache.sequence_cache import _STATE_DTYPES
+                cache += n_slots * _numel(spec.shape) * _elem(_STATE_DTYPES[spec.dtype])
     rows = int(step_tokens) if step_tokens else min(max(int(max_tokens), 1), 2048)
     hidden = model.hidden_size
     widest = max([hidden] + [_numel(s.shape) // max(1, s.shape[-1]) for s in specs.values() if len(s.shape) == 2

@@ -17,6 +17,12 @@ Roles and their ``forward``:
 * ``embedding``: ``forward(ctx, tokens, out)``; writes float32 rows.
 * ``head``:      ``forward(ctx, x, out)``; writes float32 logits.
 * ``block``:     the arrangement of norm, mixer, norm, feed-forward: ``forward(ctx, h)``.
+* ``shift``:     stands between a layer's first norm and its mixer: ``forward(ctx, x) -> x'`` mixes
+                 every row with the row before it of the same sequence (its ``cache_spec()`` keeps
+                 the last row of a step).
+* ``pass_input``: ``forward(ctx, h, base, number)``; changes the residual stream in place before
+                 pass ``number`` of a stretch of layers that runs several times (``base``: the
+                 embedding output).
 """
 from __future__ import annotations
 
@@ -27,15 +33,18 @@ import torch
 from ..config.plan import PartSpec
 from ..errors import ConfigError
 
-ROLES = ("norm", "mixer", "ffn", "position", "embedding", "head", "block")
+ROLES = ("norm", "mixer", "ffn", "position", "embedding", "head", "block", "shift", "pass_input")
 
 
 @dataclass(frozen=True)
 class TensorSpec:
     """A tensor a part needs: its shape and how random weights are drawn for it
-    ("linear" and "embedding": N(0, 0.02); "norm": 1 + N(0, 0.02))."""
+    ("linear" and "embedding": N(0, 0.02); "norm": 1 + N(0, 0.02); further rules in
+    ``weights.random_init.INIT``). ``free_dims``: axes whose size the stored tensor decides (the
+    shape given here is then only what random weights are drawn with)."""
     shape: tuple
     init: str = "linear"
+    free_dims: tuple = ()
 
 
 class Part:

@@ -11,12 +11,14 @@ class PreNormBlock(Part):
     def __init__(self, layer_spec):
         super().__init__({}, "")
         self.norm1 = build_part("norm", layer_spec.norm1)
+        self.shift = build_part("shift", layer_spec.shift) if layer_spec.shift is not None else None
         self.mixer = build_part("mixer", layer_spec.mixer)
-        self.norm2 = build_part("norm", layer_spec.norm2)
-        self.ffn = build_part("ffn", layer_spec.ffn)
+        # a layer without a feed-forward has only the first sublayer
+        self.ffn = build_part("ffn", layer_spec.ffn) if layer_spec.ffn is not None else None
+        self.norm2 = build_part("norm", layer_spec.norm2) if self.ffn is not None else None
 
     def parts(self):
-        return (self.norm1, self.mixer, self.norm2, self.ffn)
+        return tuple(p for p in (self.norm1, self.shift, self.mixer, self.norm2, self.ffn) if p is not None)
 
     def tensor_specs(self):
         out = {}
@@ -37,7 +39,9 @@ class PreNormBlock(Part):
         return all(p.graph_safe_any_step for p in self.parts())
 
     def cache_spec(self):
-        return self.mixer.cache_spec()
+        if self.shift is None:
+            return self.mixer.cache_spec()
+        return [self.mixer.cache_spec(), self.shift.cache_spec()]
 
     def query_tile_sizes(self):
         return self.mixer.query_tile_sizes()
@@ -49,10 +53,16 @@ class PreNormBlock(Part):
         # from outside the library, graph safe or not, reads and writes complete rows.
         # A part that declares ``accepts_row_scale`` takes ``ctx.take_row_scale()`` and applies
         # it, which lets the norm before it run inside the product before that.
+        # A shift part between the first norm and the mixer reads complete rows (no scale left undone).
         for norm, part in ((self.norm1, self.mixer), (self.norm2, self.ffn)):
+            if part is None:
+                continue
+            shift = self.shift if part is self.mixer else None
             if not norm.handles_pending:
                 ctx.settle(h)
-            x = norm.forward(ctx, h, allow_row_scale=part.accepts_row_scale)
+            x = norm.forward(ctx, h, allow_row_scale=part.accepts_row_scale and shift is None)
+            if shift is not None:
+                x = shift.forward(ctx, x)
             if not part.handles_pending:
                 ctx.settle(h)
             part.forward(ctx, x, h)

@@ -31,9 +31,53 @@ class TokenEmbedding(Part):
         ops.embed_gather(self.weight, tokens, out, err)
 
 
+@register_part("embedding", "bigram_embedding")
+class BigramEmbedding(Part):
+    """Token embedding plus a row of a second table picked by a hash of the previous and the
+    current token: row (previous * mul_prev + current * mul_cur) mod buckets, and row ``buckets``
+    (the table's last) for a sequence's first token. The previous token is per-sequence state:
+    the step's last token is kept for the next step. Without ``bigram_tensor`` it is a plain
+    embedding whose table has the name ``tensor``."""
+    graph_safe = True
+    graph_safe_any_step = True
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.vocab_size = int(params["vocab_size"])
+        self.hidden_size = int(params["hidden_size"])
+        self.tensor = params.get("tensor") or self.prefix + "weight"
+        self.bigram_tensor = params.get("bigram_tensor")
+        self.buckets = int(params["buckets"]) if self.bigram_tensor else 0
+        self.mul_prev = int(params["mul_prev"]) if self.bigram_tensor else 0
+        self.mul_cur = int(params["mul_cur"]) if self.bigram_tensor else 0
+        self.weight = None
+        self.bigram = None
+
+    def tensor_specs(self):
+        specs = {self.tensor: TensorSpec((self.vocab_size, self.hidden_size), "embedding")}
+        if self.bigram_tensor:
+            specs[self.bigram_tensor] = TensorSpec((self.buckets + 1, self.hidden_size), "embedding")
+        return specs
+
+    def load(self, tensors, device, dtype):
+        self.weight = to_device(tensors[self.tensor], device, dtype)
+        if self.bigram_tensor:
+            self.bigram = to_device(tensors[self.bigram_tensor], device, dtype)
+
+    def cache_spec(self):
+        from ..cache.book import StateSpec
+        return StateSpec((1,), "int32", "previous_token") if self.bigram_tensor else None
+
+    def forward(self, ctx, tokens, out, err):
+        prev = ctx.state("previous_token").view(-1) if self.bigram_tensor else None
+        ops.bigram_embed(self.weight, self.bigram, tokens, ctx.row_seq, ctx.row_pos, ctx.seq_row0, ctx.seq_new, ctx.seq_slot,
+                         prev, out, ctx.n_seqs, self.buckets, self.mul_prev, self.mul_cur, err)
+
+
 @register_part("head", "lm_head")
 class OutputProjection(Part):
-    """logits = x W^T in float32, without bias, soft-cap or scale (src/inference.rs:4284-4290)."""
+    """logits = x W^T in float32, without bias or scale (src/inference.rs:4284-4290); with
+    ``softcap`` c the logits become c tanh(logits / c). ``tensor`` names the matrix in full."""
     graph_safe = True
     graph_safe_any_step = True
 
@@ -42,18 +86,22 @@ class OutputProjection(Part):
         self.vocab_size = int(params["vocab_size"])
         self.hidden_size = int(params["hidden_size"])
         self.tied_to = params.get("tied_to")
+        self.tensor = params.get("tensor") or self.prefix + "weight"
+        self.softcap = float(params["softcap"]) if params.get("softcap") else None
         self.weight = None
 
     def tensor_specs(self):
         if self.tied_to:
             return {}
-        return {self.prefix + "weight": TensorSpec((self.vocab_size, self.hidden_size))}
+        return {self.tensor: TensorSpec((self.vocab_size, self.hidden_size))}
 
     def load(self, tensors, device, dtype, tied_weight: torch.Tensor | None = None):
         if self.tied_to:
             self.weight = tied_weight
         else:
-            self.weight = to_device(tensors[self.prefix + "weight"], device, dtype)
+            self.weight = to_device(tensors[self.tensor], device, dtype)
 
     def forward(self, ctx, x, out):
         linear.linear(ctx, x, self.weight, out, linear.STORE_F32)
+        if self.softcap is not None:
+            ops.softcap_(out, self.softcap)

@@ -1,9 +1,10 @@
-"""SwiGLU feed-forward: g = x Wg^T, u = x Wu^T, act = (g / (1 + exp(-g))) * u,
+"""Feed-forwards. SwiGLU: g = x Wg^T, u = x Wu^T, act = (g / (1 + exp(-g))) * u,
 d = act Wd^T, added into the residual stream (src/inference.rs:9657-9664, :6654-6706;
 device twin silu_mul at src/cuda_resident.rs:1769). Gate and up are one packed matrix so
 that one product makes both and the activation happens in its epilogue."""
 from __future__ import annotations
 
+from ..csrc import ops
 from . import linear
 from .base import Part, TensorSpec, register_part, to_device
 
@@ -41,4 +42,35 @@ class SwiGLU(Part):
     def forward(self, ctx, x, residual):
         act = ctx.buffer("ffn_act", (ctx.n_rows, self.intermediate_size))
         linear.linear(ctx, x, self.w_gate_up, act, linear.SWIGLU, self.group, row_scale=ctx.take_row_scale())
+        linear.add_into_residual(ctx, act, self.w_down, residual, "down_partial")
+
+
+@register_part("ffn", "dense_gelu")
+class DenseGelu(Part):
+    """d = gelu(x Wu^T) Wd^T with the tanh form of GELU, added into the residual stream. Tensors
+    ``up`` [intermediate, hidden] and ``down`` [hidden, intermediate] under the prefix."""
+    graph_safe = True
+    graph_safe_any_step = True
+    handles_pending = True
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden_size = int(params["hidden_size"])
+        self.intermediate_size = int(params["intermediate_size"])
+        self.w_up = None
+        self.w_down = None
+
+    def tensor_specs(self):
+        p = self.prefix
+        return {p + "up": TensorSpec((self.intermediate_size, self.hidden_size)),
+                p + "down": TensorSpec((self.hidden_size, self.intermediate_size))}
+
+    def load(self, tensors, device, dtype):
+        self.w_up = to_device(tensors[self.prefix + "up"], device, dtype)
+        self.w_down = to_device(tensors[self.prefix + "down"], device, dtype)
+
+    def forward(self, ctx, x, residual):
+        act = ctx.buffer("ffn_act", (ctx.n_rows, self.intermediate_size))
+        linear.linear(ctx, x, self.w_up, act, linear.STORE)
+        ops.gelu_tanh_(act)
         linear.add_into_residual(ctx, act, self.w_down, residual, "down_partial")

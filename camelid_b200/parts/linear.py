@@ -163,6 +163,17 @@ def partial_sums(ctx, x: torch.Tensor, w: torch.Tensor, name: str, row_scale=Non
     return part
 
 
+def product_f32(ctx, x: torch.Tensor, w: torch.Tensor, name: str) -> torch.Tensor:
+    """x @ w.T in float32 in the step's buffer ``name``: split sums [splits, rows, out] where the
+    step's size splits K (the reader adds them in split order), else [rows, out]."""
+    part = partial_sums(ctx, x, w, name)
+    if part is not None:
+        return part
+    out = ctx.buffer(name, (x.shape[0], w.shape[0]), torch.float32)
+    linear(ctx, x, w, out, STORE_F32)
+    return out
+
+
 def add_into_residual(ctx, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, name: str) -> None:
     """residual += x @ w.T. On the decode path the split sums are left pending on the context
     and the next norm adds them. A product of many rows on the tensor cores is *deferred*: the

@@ -20,13 +20,14 @@ class RMSNorm(Part):
         super().__init__(params, prefix)
         self.hidden_size = int(params["hidden_size"])
         self.eps = float(params["eps"])
+        self.tensor = params.get("tensor") or self.prefix + "weight"      # the weight's full name
         self.weight = None
 
     def tensor_specs(self):
-        return {self.prefix + "weight": TensorSpec((self.hidden_size,), "norm")}
+        return {self.tensor: TensorSpec((self.hidden_size,), "norm")}
 
     def load(self, tensors, device, dtype):
-        w = tensors[self.prefix + "weight"]
+        w = tensors[self.tensor]
         # a weight stored in 32-bit stays so; a 16-bit one becomes float32 only on the float32 path
         keep = None if w.dtype == torch.float32 else dtype
         self.weight = to_device(w, device, keep)

@@ -27,7 +27,9 @@ def check_tensors(specs: dict, names_shapes_dtypes: dict, *, tolerated: tuple = 
     for n, spec in specs.items():
         if n in names_shapes_dtypes:
             shape, dtype = names_shapes_dtypes[n]
-            if tuple(shape) != tuple(spec.shape):
+            free = getattr(spec, "free_dims", ())
+            if len(shape) != len(spec.shape) or any(int(a) != int(b) for i, (a, b) in enumerate(zip(shape, spec.shape))
+                                                    if i not in free):
                 wrong.append((n, spec.shape, shape))
             if dtype not in _FLOATS:
                 other.append(f"{n}: stored as {dtype}, expected a floating-point type")

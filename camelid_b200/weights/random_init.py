@@ -21,17 +21,28 @@ from . import counter_random
 from .safetensors_io import write_safetensors
 
 STD = 0.02
+# init rule -> (mean, standard deviation). Besides matrices and norm weights: small positive
+# numbers (mixing weights, rates of a distance penalty), gate biases that keep a memory
+# (forget) or leave it alone (input), logarithms of decay rates and their step-size biases,
+# taps of a short convolution.
+INIT = {"linear": (0.0, STD), "embedding": (0.0, STD), "norm": (1.0, STD), "fraction": (0.3, 0.05),
+        "forget_bias": (4.0, 0.5), "input_bias": (0.0, 0.3), "log_rate": (-2.0, 0.5), "conv": (0.25, 0.3),
+        "low_rank": (0.0, 0.1)}
 
 
 def mean_of(init: str) -> float:
-    return 1.0 if init == "norm" else 0.0
+    return INIT[init][0]
+
+
+def std_of(init: str) -> float:
+    return INIT[init][1]
 
 
 def random_slice(name: str, init: str, seed: int, first: int, count: int) -> torch.Tensor:
     """float32 values of elements ``first .. first + count`` (row-major) of tensor ``name``,
     computed on the host."""
     key = counter_random.tensor_key(seed, name)
-    return torch.from_numpy(counter_random.fill_host(key, first, count, mean_of(init), STD))
+    return torch.from_numpy(counter_random.fill_host(key, first, count, mean_of(init), std_of(init)))
 
 
 def random_tensor(name: str, spec, seed: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
@@ -39,7 +50,7 @@ def random_tensor(name: str, spec, seed: int, dtype: torch.dtype, device="cpu") 
     if torch.device(device).type == "cuda":
         from ..csrc import ops
         out = torch.empty(shape, dtype=dtype, device=device)
-        ops.random_fill(out, counter_random.tensor_key(seed, name), 0, mean_of(spec.init), STD)
+        ops.random_fill(out, counter_random.tensor_key(seed, name), 0, mean_of(spec.init), std_of(spec.init))
         return out
     n = 1
     for s in shape:
