@@ -60,42 +60,41 @@ def token_shift(h, shift):
     return h + (prev - h) * shift
 
 
-def window_attention(h, P, p, m, eps):
-    """Grouped-query attention without rotation: per-head RMS norm of q and k, a logarithmic
-    distance penalty, a sliding window, softmax, an output gate."""
-    T = h.shape[0]
-    H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ P[p + "q"].T).view(T, H, D)
-    k = (h @ P[p + "k"].T).view(T, G, D)
-    v = (h @ P[p + "v"].T).view(T, G, Dv)
-    q = rms_norm(q, P[p + "q.norm"], eps)
-    k = rms_norm(k, P[p + "k.norm"], eps)
-    out = torch.zeros(T, H, Dv, dtype=F64)
-    window = m["mask"]["size"]
+def window_scores_core(q, k, v, scale, window, r1, r2):
+    """q [T, H, D], k [T, G, D], v [T, G, Dv] -> [T, H, Dv]: softmax over the last ``window`` keys of
+    (q . k) scale - r1 ln(1 + r2 distance)."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    out = torch.zeros(T, H, v.shape[2], dtype=F64)
     for i in range(T):
         lo = max(0, i - window + 1)
         for hd in range(H):
             g = hd // (H // G)
             dist = torch.arange(i - lo, -1, -1, dtype=F64)                  # i - j for j = lo..i
-            s = (k[lo:i + 1, g] @ q[i, hd]) * m["scale"] - P[p + "r1"][hd] * torch.log1p(P[p + "r2"][hd] * dist)
-            w = torch.softmax(s, 0)
-            out[i, hd] = w @ v[lo:i + 1, g]
+            s = (k[lo:i + 1, g] @ q[i, hd]) * scale - r1[hd] * torch.log1p(r2[hd] * dist)
+            out[i, hd] = torch.softmax(s, 0) @ v[lo:i + 1, g]
+    return out
+
+
+def window_attention(h, P, p, m, eps):
+    """Grouped-query attention without rotation: per-head RMS norm of q and k, a logarithmic
+    distance penalty, a sliding window, softmax, an output gate."""
+    T = h.shape[0]
+    H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    q = rms_norm((h @ P[p + "q"].T).view(T, H, D), P[p + "q.norm"], eps)
+    k = rms_norm((h @ P[p + "k"].T).view(T, G, D), P[p + "k.norm"], eps)
+    v = (h @ P[p + "v"].T).view(T, G, Dv)
+    out = window_scores_core(q, k, v, m["scale"], m["mask"]["size"], P[p + "r1"], P[p + "r2"])
     gate = torch.sigmoid(h @ P[p + "g"].T)
     return (out.reshape(T, H * Dv) * gate) @ P[p + "o"].T
 
 
-def matrix_memory(h, P, p, m, eps):
-    """The matrix memory with exponential gates and a running maximum that starts at zero."""
-    T = h.shape[0]
-    H, D, Dv, cap = m["heads"], m["dim"], m["vdim"], m["gate_cap"]
-    q = (h @ P[p + "q"].T).view(T, H, D) * D ** -0.5
-    k = (h @ P[p + "k"].T).view(T, H, D)
-    v = (h @ P[p + "v"].T).view(T, H, Dv)
-    gi = cap * torch.tanh((h @ P[p + "i"].T + P[p + "i.b"]) / cap)
-    gf = logsigmoid(cap * torch.tanh((h @ P[p + "f"].T + P[p + "f.b"]) / cap))
-    out = torch.zeros(T, H, Dv, dtype=F64)
+def matrix_memory_core(q, k, v, gi, gf):
+    """q, k [T, H, D] (q already scaled), v [T, H, Dv], log gates gi, gf [T, H] -> S^T q / denominator."""
+    T, H, D = q.shape
+    out = torch.zeros(T, H, v.shape[2], dtype=F64)
     for hd in range(H):
-        S = torch.zeros(D, Dv, dtype=F64)
+        S = torch.zeros(D, v.shape[2], dtype=F64)
         n = torch.zeros(D, dtype=F64)
         mx = 0.0
         for t in range(T):
@@ -107,6 +106,19 @@ def matrix_memory(h, P, p, m, eps):
             mx = m_new
             den = max(abs(float(n @ q[t, hd])), math.exp(-mx)) + 1e-6
             out[t, hd] = (S.T @ q[t, hd]) / den
+    return out
+
+
+def matrix_memory(h, P, p, m, eps):
+    """The matrix memory with exponential gates and a running maximum that starts at zero."""
+    T = h.shape[0]
+    H, D, Dv, cap = m["heads"], m["dim"], m["vdim"], m["gate_cap"]
+    q = (h @ P[p + "q"].T).view(T, H, D) * D ** -0.5
+    k = (h @ P[p + "k"].T).view(T, H, D)
+    v = (h @ P[p + "v"].T).view(T, H, Dv)
+    gi = cap * torch.tanh((h @ P[p + "i"].T + P[p + "i.b"]) / cap)
+    gf = logsigmoid(cap * torch.tanh((h @ P[p + "f"].T + P[p + "f.b"]) / cap))
+    out = matrix_memory_core(q, k, v, gi, gf)
     out = rms_norm(out, None, eps).reshape(T, H * Dv) * P[p + "norm"]
     return (out * torch.sigmoid(h @ P[p + "g"].T)) @ P[p + "o"].T
 
@@ -131,6 +143,22 @@ def unit(x):
     return x / torch.sqrt((x * x).sum(-1, keepdim=True) + 1e-6)
 
 
+def delta_core(q, k, v, beta, decay):
+    """q, k [T, G, D] unit vectors (q scaled), v [T, H, Dv], beta [T, H], decay [T, H, D] -> S^T q."""
+    T, G, D = q.shape
+    H, Dv = v.shape[1], v.shape[2]
+    out = torch.zeros(T, H, Dv, dtype=F64)
+    for hd in range(H):
+        g = hd // (H // G)
+        S = torch.zeros(D, Dv, dtype=F64)
+        for t in range(T):
+            S = decay[t, hd].unsqueeze(1) * S
+            u = beta[t, hd] * (v[t, hd] - S.T @ k[t, g])
+            S = S + torch.outer(k[t, g], u)
+            out[t, hd] = S.T @ q[t, g]
+    return out
+
+
 def channel_delta(h, P, p, m, eps):
     """Gated delta rule with one decay per head and key channel."""
     T = h.shape[0]
@@ -143,15 +171,7 @@ def channel_delta(h, P, p, m, eps):
     beta = torch.sigmoid(h @ P[p + "b"].T)
     a = (h @ P[p + "a1"].T) @ P[p + "a2"].T + P[p + "dt_bias"]
     decay = torch.exp(-torch.exp(P[p + "A_log"]).view(1, H, 1) * softplus(a).view(T, H, D))
-    out = torch.zeros(T, H, Dv, dtype=F64)
-    for hd in range(H):
-        g = hd // (H // G)
-        S = torch.zeros(D, Dv, dtype=F64)
-        for t in range(T):
-            S = decay[t, hd].unsqueeze(1) * S
-            u = beta[t, hd] * (v[t, hd] - S.T @ k[t, g])
-            S = S + torch.outer(k[t, g], u)
-            out[t, hd] = S.T @ q[t, g]
+    out = delta_core(q, k, v, beta, decay)
     out = rms_norm(out, P[p + "norm"], eps).reshape(T, H * Dv)
     gate = torch.sigmoid((h @ P[p + "g1"].T) @ P[p + "g2"].T)
     return (out * gate) @ P[p + "o"].T
