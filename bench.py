@@ -5,6 +5,8 @@ One JSON line: decode tokens a second of the Llama 3.2 1B shape (random weights,
 same end to end through the Python entry point, the prefill of 2,048 tokens, the roofline
 fraction of the decode step, decode at batch 1 and 64 (``points``, with time, bytes and
 fraction in ``points_detail``), and the float32 model's decode step and prefill (``fp32``).
+``--fomatar small,medium`` measures another workload instead (the default one stays as it is): the Fomatar
+decoder beside the dense decoder of equal width, depth and feed-forward size.
 This library runs on one GPU: for --gpus above 1 it says so and exits with 2."""
 import argparse
 import json
@@ -31,6 +33,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-fp32", action="store_true", help="leave out the float32 model's figures")
+    ap.add_argument("--fomatar", default=None, metavar="SIZES",
+                    help="instead of the default workload: decode and prefill of the Fomatar decoder beside the dense "
+                         "decoder of equal size, e.g. small,medium,wide (prompts of 512 tokens, --batch, --steps)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
@@ -40,6 +45,10 @@ def main() -> int:
             print(f"camelid_b200 is a single-GPU library: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
     from camelid_b200 import benchmark
+    if args.fomatar:
+        print(json.dumps(benchmark.run_fomatar(tuple(args.fomatar.split(",")), batch=args.batch, steps=min(args.steps, 64),
+                                               warmup=max(min(args.warmup, 8), 3), dtype=args.dtype)))
+        return 0
     rec = benchmark.run(batch=args.batch, prompt_tokens=args.prompt_tokens, decode_steps=args.steps,
                         warmup=max(args.warmup, 3), dtype=args.dtype, layers=args.layers, config_index=args.config,
                         points=not args.no_points, e2e=not args.no_e2e,

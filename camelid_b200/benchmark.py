@@ -387,6 +387,126 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
     return rec
 
 
+# ---------------------------------------------------------------------------------------
+# Fomatar beside the dense Llama decoder at equal width, depth and feed-forward size
+
+FOMATAR_SIZES = {
+    # width, layers (channel_delta and parallel in turn; every parallel layer has the feed-forward),
+    # heads of `head` channels, window of the attention branch
+    "small": dict(width=1024, layers=8, ff=4096, heads=8, kv_heads=2, head=128, window=512, vocab=32768),
+    "medium": dict(width=2048, layers=16, ff=8192, heads=16, kv_heads=4, head=128, window=1024, vocab=32768),
+    "wide": dict(width=4096, layers=8, ff=14336, heads=32, kv_heads=8, head=128, window=1024, vocab=32768),
+}
+
+
+def fomatar_config_for(size: str) -> dict:
+    s = FOMATAR_SIZES[size]
+    heads, head = s["heads"], s["head"]
+    layers = []
+    for i in range(s["layers"]):
+        if i % 2 == 0:
+            layers.append({"type": "channel_delta", "mlp": None,
+                           "mixer": {"conv": 4, "dim": head, "vdim": head, "heads": heads, "kv_heads": heads, "rank": 64}})
+        else:
+            layers.append({"type": "parallel", "mlp": {"kind": "dense", "ff": s["ff"]},
+                           "mixer": {"left": {"dim": head, "vdim": head, "heads": heads, "kv_heads": s["kv_heads"],
+                                              "mask": {"size": s["window"]}, "scale": head ** -0.5},
+                                     "right": {"dim": head, "vdim": head, "heads": heads // 2, "gate_cap": 15.0}}})
+    return {"architecture": "Fomatar", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}},
+            "layers": layers}
+
+
+def llama_config_like(size: str) -> dict:
+    """The dense Llama decoder of the same width, depth, feed-forward size, heads and vocabulary."""
+    s = FOMATAR_SIZES[size]
+    return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "max_position_embeddings": 131072,
+            "num_hidden_layers": s["layers"], "hidden_size": s["width"], "num_attention_heads": s["heads"],
+            "num_key_value_heads": s["kv_heads"], "head_dim": s["head"], "intermediate_size": s["ff"],
+            "vocab_size": s["vocab"], "rope_theta": 500000.0, "rope_scaling": None, "rms_norm_eps": 1e-6,
+            "tie_word_embeddings": False}
+
+
+def model_step_bytes(lm, batch: int, context: float) -> dict:
+    """Bytes a decode step of ``batch`` sequences at ``context`` positions must move: every matrix and vector once
+    (of an embedding table only the rows it reads), the keys and values a query can see, every state read and written."""
+    from .cache.book import KVSpec, StateSpec, flatten_specs
+    from .cache.sequence_cache import _STATE_DTYPES
+    m = lm.model
+    elem = 2 if m.dtype == torch.bfloat16 else 4
+    tables = set(m.embedding.tensor_specs())
+    weights = sum(int(np.prod(sp.shape)) * elem for n, sp in m.tensor_specs().items() if n not in tables)
+    kv = state = 0
+    for needs, src in zip(m.entry_cache_specs(), m.entry_cache_sources()):
+        for sp in flatten_specs(needs):
+            if isinstance(sp, KVSpec):
+                seen = min(context, sp.window) if sp.window else context
+                kv += (0 if src is not None else 0) + batch * seen * sp.n_kv_heads * (sp.head_dim + sp.value_dim) * elem
+            elif isinstance(sp, StateSpec) and src is None:
+                state += 2 * batch * int(np.prod(sp.shape)) * torch.empty((), dtype=_STATE_DTYPES[sp.dtype]).element_size()
+    return {"weights": weights, "kv": int(kv), "state": state, "total": int(weights + kv + state)}
+
+
+def model_prefill_flops(lm, tokens: int) -> float:
+    """2 x tokens x (elements of every matrix a token passes) plus the mixers' own work: attention over the visible
+    keys, and per token and head of a recurrent mixer the update and the read-out of its matrix state."""
+    from .cache.book import KVSpec, StateSpec, flatten_specs
+    m = lm.model
+    tables = set(m.embedding.tensor_specs())
+    per_layer = {}
+    for n, sp in m.tensor_specs().items():
+        if n not in tables and len(sp.shape) == 2 and "conv" not in n and not n.startswith(("loop.", "head", "lm_head")):
+            per_layer[n] = int(np.prod(sp.shape))
+    runs = {}
+    for e in m.schedule:
+        runs[e.layer] = runs.get(e.layer, 0) + 1
+    total = 0.0
+    names = {i: [n for n in per_layer if n in m.blocks[i].tensor_specs()] for i in range(len(m.blocks))}
+    for i, r in runs.items():
+        total += 2.0 * tokens * r * sum(per_layer[n] for n in names[i])
+    for needs in m.entry_cache_specs():
+        for sp in flatten_specs(needs):
+            if isinstance(sp, KVSpec):
+                seen = min(tokens, sp.window) if sp.window else tokens / 2.0
+                heads = getattr(sp, "n_kv_heads")
+                total += 2.0 * tokens * seen * heads * (sp.head_dim + sp.value_dim)      # per kv head; query groups below
+            elif isinstance(sp, StateSpec) and sp.name == "memory":
+                total += 6.0 * tokens * int(np.prod(sp.shape))
+    return total
+
+
+def run_fomatar(sizes=("small", "medium"), batch: int = 8, prompt_tokens: int = 512, steps: int = 64, warmup: int = 4,
+                prefill_tokens: int = 2048, dtype: str = "bfloat16") -> dict:
+    """Decode steps (timed on the device in the loop ``generate`` runs) and one prefill step of the Fomatar decoder
+    and of the dense Llama decoder of equal width, depth, feed-forward size and vocabulary, random weights."""
+    from . import api
+    pk = peaks()
+    out = {"metric": "decode and prefill tokens/s, Fomatar beside the dense decoder of equal size", "dtype": dtype,
+           "batch": batch, "prompt_tokens": prompt_tokens, "steps": steps, "warmup": warmup,
+           "prefill_tokens": prefill_tokens, "peaks": pk["source"], "data": "synthetic (seeded uniform token ids, random weights)",
+           "sizes": {}}
+    for size in sizes:
+        rec = {"shape": FOMATAR_SIZES[size]}
+        for label, cfg in (("fomatar", fomatar_config_for(size)), ("llama", llama_config_like(size))):
+            lm = api.from_random(cfg, seed=7, dtype=dtype)
+            vocab = {"vocab_size": FOMATAR_SIZES[size]["vocab"]}
+            rng = np.random.default_rng(7)
+            dec = measure_decode_device(lm, vocab, batch, prompt_tokens, steps, warmup, rng)
+            bytes_step = model_step_bytes(lm, batch, dec["context"])
+            pre = measure_prefill(lm, vocab, prefill_tokens, rng)
+            flops = model_prefill_flops(lm, prefill_tokens) if label == "fomatar" else prefill_flops(cfg, prefill_tokens)
+            rec[label] = {
+                "decode_tokens_per_s": dec["value"], "decode_ms_per_step": dec["ms_per_step"], "launches_per_step": dec["launches"] / steps,
+                "decode_bytes": bytes_step, "decode_frac_of_copy": bytes_step["total"] / (dec["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"],
+                "prefill_tokens_per_s": pre["value"], "prefill_ms": pre["ms"],
+                "prefill_frac_of_gemm": flops / (pre["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12) if dtype == "bfloat16" else None,
+                "clocks": dec["clocks"]}
+            del lm
+            torch.cuda.empty_cache()
+        out["sizes"][size] = rec
+    return out
+
+
 def ablate_decode(batch: int = 8, prompt_tokens: int = 2048, dtype: str = "bfloat16", layers: int | None = None,
                   config_index: int = 2, reps: int = 50) -> dict:
     """Where a decode step's time goes: the captured step graph is timed whole, and again with

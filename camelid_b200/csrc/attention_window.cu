@@ -5,7 +5,7 @@
 //   score(i, j) = (q_i . k_j) scale - r1[head] ln(1 + r2[head] (i - j)),   0 <= i - j < window
 //
 // Two kernels. The first normalises q and k (weight per channel, shared by the heads), keeps
-// q in the compute type and writes k and v into their pages. The second gives one warp to
+// q in the compute type and writes k and v into their pages. The second gives a block to
 // every (row, head): lanes take keys for the scores (all in float), then columns of the
 // values; the softmax runs online over rounds of 32 keys, from the oldest visible key to the
 // row's own, whether the row came with a prompt or alone.
@@ -87,57 +87,95 @@ extern "C" int cml_qk_norm_kv_write(const float* proj, long ld, const void* q_w,
 
 // q [rows, heads x D]; out [rows, heads x Dv] = softmax(...) V, times sigmoid(gate) where
 // gate (float [rows, ldg], at column gate_col) is given. window <= 0: all keys. r1, r2 float
-// [heads] or null (no penalty). Dynamic shared memory: D floats per warp for the query.
-#define AW_WARPS 4
+// [heads] or null (no penalty).
+//
+// A block of NW warps owns one (row, head). The visible keys, oldest first, are dealt to the
+// warps in runs of whole rounds of 32 (how many depends on the row's position and the window
+// alone, not on how the prompt was cut); in a round a lane takes one key for the score (the key
+// row read in 16-byte pieces where its size allows) and then columns of the values; each warp
+// keeps an online softmax of its run, and the runs are merged in warp order at the end.
+// Dynamic shared memory: the query (D floats), then per warp its maximum, its sum and Dv sums.
 #define AW_MAX_VREGS 8        // value columns per lane: Dv <= 256
+
+template <typename T> struct Piece;                 // 16 bytes of a key row as floats
+template <> struct Piece<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float* f) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    }
+};
+template <> struct Piece<bf16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const bf16* p, float* f) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
 
 template <typename T>
 __global__ void window_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                                         const int* __restrict__ table, int max_blocks, const int* __restrict__ row_seq,
                                         const int* __restrict__ row_pos, const float* __restrict__ r1,
                                         const float* __restrict__ r2, const float* __restrict__ gate, long ldg, int gate_col,
-                                        T* __restrict__ out, int rows, int heads, int kv_heads, int D, int Dv, int window,
-                                        float scale) {
-    extern __shared__ float q_sh[];
+                                        T* __restrict__ out, int heads, int kv_heads, int D, int Dv, int window, float scale) {
+    extern __shared__ __align__(16) float aw_sh[];
     pdl_wait();
     pdl_launch_dependents();
-    const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int item = blockIdx.x * AW_WARPS + warp_in_block;
-    if (item >= rows * heads) return;
-    const int r = item / heads, hd = item % heads, g = hd / (heads / kv_heads);
-    float* qs = q_sh + warp_in_block * D;
-    for (int c = lane; c < D; c += 32) qs[c] = to_f32(q[((size_t)r * heads + hd) * D + c]);
-    __syncwarp();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int r = blockIdx.x / heads, hd = blockIdx.x % heads, g = hd / (heads / kv_heads);
+    float* qs = aw_sh;
+    float* part = aw_sh + ((D + 3) & ~3) + warp * (Dv + 2);
+    for (int c = threadIdx.x; c < D; c += blockDim.x) qs[c] = to_f32(q[((size_t)r * heads + hd) * D + c]);
+    __syncthreads();
     const int i = row_pos[r];
     const int lo = window > 0 ? max(0, i - window + 1) : 0;
+    const int rounds = (i - lo) / 32 + 1;
+    const int per_warp = (rounds + nw - 1) / nw;
+    const int j_first = lo + 32 * warp * per_warp, j_end = min(i + 1, j_first + 32 * per_warp);
     const int* tb = table + (size_t)row_seq[r] * max_blocks;
     const float p1 = r1 ? r1[hd] : 0.f, p2 = r2 ? r2[hd] : 0.f;
+    const bool pieces = (D % Piece<T>::N) == 0;              // a key row is a whole number of 16-byte pieces
     float m = -INFINITY, l = 0.f;
     float acc[AW_MAX_VREGS];
 #pragma unroll
     for (int e = 0; e < AW_MAX_VREGS; ++e) acc[e] = 0.f;
-    for (int j0 = lo; j0 <= i; j0 += 32) {
+    for (int j0 = j_first; j0 < j_end; j0 += 32) {
         const int j = j0 + lane;
         float sc = -INFINITY;
         int page = -1;
-        if (j <= i) {
+        if (j < j_end) {
             page = tb[j / CML_PAGE];
             if (page >= 0) {
                 const T* kr = k_pages + (((size_t)page * kv_heads + g) * CML_PAGE + j % CML_PAGE) * D;
                 float dot = 0.f;
-                for (int c = 0; c < D; ++c) dot = fmaf(qs[c], to_f32(kr[c]), dot);
+                if (pieces) {
+                    for (int c = 0; c < D; c += Piece<T>::N) {
+                        float kf[Piece<T>::N];
+                        Piece<T>::load(kr + c, kf);
+#pragma unroll
+                        for (int x = 0; x < Piece<T>::N; ++x) dot = fmaf(qs[c + x], kf[x], dot);
+                    }
+                } else {
+                    for (int c = 0; c < D; ++c) dot = fmaf(qs[c], to_f32(kr[c]), dot);
+                }
                 sc = dot * scale;
                 if (r1) sc -= p1 * log1pf(p2 * (float)(i - j));
             }
         }
-        const float m_new = fmaxf(m, warp_max(sc));               // the row's own key is always there: finite
+        const float m_new = fmaxf(m, warp_max(sc));
         const float p = sc == -INFINITY ? 0.f : expf(sc - m_new);
         const float fix = m == -INFINITY ? 0.f : expf(m - m_new);
         l = l * fix + warp_sum(p);
         m = m_new;
 #pragma unroll
         for (int e = 0; e < AW_MAX_VREGS; ++e) acc[e] *= fix;
-        const int nk = min(32, i - j0 + 1);
+        const int nk = min(32, j_end - j0);
         for (int t = 0; t < nk; ++t) {
             const float pt = __shfl_sync(0xffffffffu, p, t);
             const int pg = __shfl_sync(0xffffffffu, page, t);
@@ -150,13 +188,32 @@ __global__ void window_attention_kernel(const T* __restrict__ q, const T* __rest
             }
         }
     }
-    const float inv = 1.0f / l;
-    T* o = out + ((size_t)r * heads + hd) * Dv;
-    const float* gt = gate ? gate + (size_t)r * ldg + gate_col + hd * Dv : nullptr;
+    if (lane == 0) { part[0] = m; part[1] = l; }
 #pragma unroll
     for (int e = 0; e < AW_MAX_VREGS; ++e) {
         const int c = lane + 32 * e;
-        if (c < Dv) o[c] = from_f32<T>(acc[e] * inv * (gt ? sigmoid_w(gt[c]) : 1.0f));
+        if (c < Dv) part[2 + c] = acc[e];
+    }
+    __syncthreads();
+    // the runs merged in warp order (warp 0 always has the oldest visible key, so the maximum is finite)
+    const float* parts = aw_sh + ((D + 3) & ~3);
+    float top = -INFINITY;
+    for (int w = 0; w < nw; ++w) top = fmaxf(top, parts[w * (Dv + 2)]);
+    float total = 0.f;
+    for (int w = 0; w < nw; ++w) {
+        const float mw = parts[w * (Dv + 2)];
+        if (mw != -INFINITY) total += parts[w * (Dv + 2) + 1] * expf(mw - top);
+    }
+    const float inv = 1.0f / total;
+    T* o = out + ((size_t)r * heads + hd) * Dv;
+    const float* gt = gate ? gate + (size_t)r * ldg + gate_col + hd * Dv : nullptr;
+    for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
+        float sum = 0.f;
+        for (int w = 0; w < nw; ++w) {
+            const float mw = parts[w * (Dv + 2)];
+            if (mw != -INFINITY) sum += parts[w * (Dv + 2) + 2 + c] * expf(mw - top);
+        }
+        o[c] = from_f32<T>(sum * inv * (gt ? sigmoid_w(gt[c]) : 1.0f));
     }
 }
 
@@ -166,18 +223,19 @@ extern "C" int cml_window_attention(const void* q, const void* k_pages, const vo
                                     int D, int Dv, int window, float scale, void* stream) {
     if (rows <= 0) return 0;
     if (Dv > 32 * AW_MAX_VREGS || D < 1 || heads % kv_heads) return CML_ERR_BAD_SIZE;
-    const long items = (long)rows * heads;
-    dim3 grid((unsigned)((items + AW_WARPS - 1) / AW_WARPS));
-    const size_t smem = (size_t)AW_WARPS * D * sizeof(float);
-    if (smem > 48 * 1024) return CML_ERR_BAD_SIZE;
+    // warps per (row, head): one per 64 keys of the window, at most 8; fixed by the window alone
+    const int nw = window > 0 ? (window + 63) / 64 < 8 ? (window + 63) / 64 : 8 : 8;
+    dim3 grid((unsigned)((long)rows * heads));
+    const size_t smem = (size_t)(((D + 3) & ~3) + nw * (Dv + 2)) * sizeof(float);
+    if (smem > 48 * 1024 || (long)rows * heads > 0x7fffffffL) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == CML_DTYPE_F32)
-        launch_pdl(window_attention_kernel<float>, grid, dim3(32 * AW_WARPS), smem, s, (const float*)q, (const float*)k_pages,
-                   (const float*)v_pages, table, max_blocks, row_seq, row_pos, r1, r2, gate, ldg, gate_col, (float*)out, rows,
+        launch_pdl(window_attention_kernel<float>, grid, dim3(32 * nw), smem, s, (const float*)q, (const float*)k_pages,
+                   (const float*)v_pages, table, max_blocks, row_seq, row_pos, r1, r2, gate, ldg, gate_col, (float*)out,
                    heads, kv_heads, D, Dv, window, scale);
     else if (dtype == CML_DTYPE_BF16)
-        launch_pdl(window_attention_kernel<bf16>, grid, dim3(32 * AW_WARPS), smem, s, (const bf16*)q, (const bf16*)k_pages,
-                   (const bf16*)v_pages, table, max_blocks, row_seq, row_pos, r1, r2, gate, ldg, gate_col, (bf16*)out, rows,
+        launch_pdl(window_attention_kernel<bf16>, grid, dim3(32 * nw), smem, s, (const bf16*)q, (const bf16*)k_pages,
+                   (const bf16*)v_pages, table, max_blocks, row_seq, row_pos, r1, r2, gate, ldg, gate_col, (bf16*)out,
                    heads, kv_heads, D, Dv, window, scale);
     else
         return CML_ERR_BAD_DTYPE;

@@ -93,8 +93,8 @@ _SIGNATURES = {
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                        c_int, c_void_p],
     ("recurrence", "cml_memory_scan"): [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
-                                        c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                        c_int, c_int, c_void_p],
+                                        c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                        c_int, c_int, c_int, c_void_p],
     ("recurrence", "cml_head_norm_gate"): [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_long, c_int, c_void_p, c_int,
                                            c_int, c_int, c_int, c_float, c_void_p],
     ("attention_window", "cml_qk_norm_kv_write"): [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p,
@@ -417,12 +417,12 @@ def conv_unit(proj: torch.Tensor, conv_w: torch.Tensor, state: torch.Tensor, row
 def delta_scan(qkv: torch.Tensor, beta_in: torch.Tensor, beta_col: int, decay_in: torch.Tensor, a_log, dt_bias,
                state: torch.Tensor, seq_row0, seq_new, seq_start, seq_slot, out: torch.Tensor, n_seqs: int, heads: int,
                qk_heads: int, key_dim: int, value_dim: int):
-    """The gated delta rule over each sequence's new rows; ``state`` float32 [slots, heads, key_dim,
-    value_dim] is read and replaced; ``out`` float32 [rows, heads * value_dim] = S^T q."""
+    """The gated delta rule over each sequence's new rows; ``state`` float32 [slots, heads, value_dim,
+    key_dim] (column by column) is read and replaced; ``out`` float32 [rows, heads * value_dim] = S^T q."""
     _dev(qkv, beta_in, decay_in, a_log, dt_bias, state, seq_row0, seq_new, seq_start, seq_slot, out)
     for t in (qkv, beta_in, decay_in, out, state, a_log, dt_bias):
         assert t.dtype == torch.float32 and t.stride(-1) == 1
-    assert state.is_contiguous() and state.shape[1:] == (heads, key_dim, value_dim) and out.is_contiguous()
+    assert state.is_contiguous() and state.shape[1:] == (heads, value_dim, key_dim) and out.is_contiguous()
     assert decay_in.shape[1] == heads * key_dim and out.shape[1] == heads * value_dim
     _check(_fn("recurrence", "cml_delta_scan")(_p(qkv), qkv.stride(0), _p(beta_in), beta_in.stride(0), beta_col, _p(decay_in),
                                                decay_in.stride(0), _p(a_log), _p(dt_bias), _p(state), _p(seq_row0),
@@ -430,19 +430,22 @@ def delta_scan(qkv: torch.Tensor, beta_in: torch.Tensor, beta_col: int, decay_in
                                                key_dim, value_dim, _stream()), "delta_scan")
 
 
-def memory_scan(proj: torch.Tensor, cols: tuple, i_bias, f_bias, cap: float, q_scale: float, state: torch.Tensor, seq_row0,
-                seq_new, seq_start, seq_slot, out: torch.Tensor, n_seqs: int, heads: int, key_dim: int, value_dim: int):
+def memory_scan(proj: torch.Tensor, cols: tuple, i_bias, f_bias, cap: float, q_scale: float, state: torch.Tensor,
+                state_m: torch.Tensor, seq_row0, seq_new, seq_start, seq_slot, out: torch.Tensor, n_seqs: int, heads: int,
+                key_dim: int, value_dim: int):
     """The matrix memory with exponential gates over each sequence's new rows. ``cols``: columns of
     q, k, v, input gate, forget gate in ``proj`` (float32). ``state`` float32 [slots, heads,
-    key_dim + 1, value_dim + 1]; ``out`` float32 [rows, heads, value_dim + 2]."""
-    _dev(proj, i_bias, f_bias, state, seq_row0, seq_new, seq_start, seq_slot, out)
-    for t in (proj, i_bias, f_bias, state, out):
+    value_dim + 1, key_dim] (column by column, the last column is n), ``state_m`` float32 [slots, heads,
+    value_dim + 1] (the running maximum); ``out`` float32 [rows, heads, value_dim + 2]."""
+    _dev(proj, i_bias, f_bias, state, state_m, seq_row0, seq_new, seq_start, seq_slot, out)
+    for t in (proj, i_bias, f_bias, state, state_m, out):
         assert t.dtype == torch.float32 and t.stride(-1) == 1
-    assert state.is_contiguous() and state.shape[1:] == (heads, key_dim + 1, value_dim + 1)
+    assert state.is_contiguous() and state.shape[1:] == (heads, value_dim + 1, key_dim)
+    assert state_m.is_contiguous() and state_m.shape[1:] == (heads, value_dim + 1)
     assert out.is_contiguous() and out.shape[1:] == (heads, value_dim + 2)
     q_col, k_col, v_col, i_col, f_col = cols
     _check(_fn("recurrence", "cml_memory_scan")(_p(proj), proj.stride(0), q_col, k_col, v_col, i_col, f_col, _p(i_bias),
-                                                _p(f_bias), float(cap), float(q_scale), _p(state), _p(seq_row0), _p(seq_new),
+                                                _p(f_bias), float(cap), float(q_scale), _p(state), _p(state_m), _p(seq_row0), _p(seq_new),
                                                 _p(seq_start), _p(seq_slot), _p(out), n_seqs, heads, key_dim, value_dim,
                                                 _stream()), "memory_scan")
 

@@ -7,18 +7,16 @@
 //                                                  S <- e^(f + m - m') S + e^(i - m') k v^T  (n likewise with k alone);
 //                                                  o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)
 //
-// Both are independent per column of S: a thread owns one column (key_dim floats in
-// registers) of one (sequence, head) and walks the sequence's new tokens in order, so a
-// prompt's rows and the same rows fed one by one are summed in the same order. The matrix
-// memory keeps n as one more column (whose v is 1) and m as one more row, per column, so
+// Both are independent per column of S: eight threads of a warp share one column (a slice of
+// the key axis each, in registers) of one (sequence, head) and walk the sequence's new tokens
+// in order, so a prompt's rows and the same rows fed one by one are summed in the same order.
+// The matrix memory keeps n as one more column (whose v is 1) and a copy of m per column, so
 // that no thread reads what another writes. q, k, gates of a few tokens at a time are staged
 // in shared memory by the whole block.
 //
 // Before them: the short causal convolution with SiLU and the unit norm of q and k for the
 // delta rule. After them: the per-head RMS norm with weight and sigmoid gate.
 #include "common.cuh"
-
-#define REC_TOKENS 8          // tokens staged per round
 
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
@@ -84,178 +82,242 @@ extern "C" int cml_conv_unit(const float* proj, long ld, const float* conv_w, co
 }
 
 // ------------------------------------------------------------------------------------
-// Gated delta rule. qkv [rows, ldq]: unit q (qk_heads x D), unit k, v (heads x Dv) from
-// conv_unit_kernel. beta_in [rows, ldb] at column beta_col + head: before the sigmoid.
-// decay_in [rows, ldd] (heads x D): before dt_bias; g = exp(-exp(a_log[head]) softplus(x + dt_bias)).
-// state [slots, heads, D, Dv]. out [rows, heads x Dv] float, S^T q.
-template <int DMAX>
-__global__ void __launch_bounds__(128) delta_scan_kernel(
-        const float* __restrict__ qkv, long ldq, const float* __restrict__ beta_in, long ldb, int beta_col,
-        const float* __restrict__ decay_in, long ldd, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
-        float* __restrict__ state, const int* __restrict__ seq_row0, const int* __restrict__ seq_new,
-        const int* __restrict__ seq_start, const int* __restrict__ seq_slot, float* __restrict__ out, int heads,
-        int qk_heads, int D, int Dv) {
-    __shared__ float sq[REC_TOKENS][DMAX], sk[REC_TOKENS][DMAX], sg[REC_TOKENS][DMAX];
-    __shared__ float sv[REC_TOKENS][128], sbeta[REC_TOKENS];
+// The scans. A block of 128 threads owns 16 columns of one (sequence, head); the key axis of a
+// column is cut into 8 slices of DS channels, one thread each, the 8 threads of a column in one
+// warp (lane = 8 * column + slice), so that a dot product over the key axis is DS multiply-adds
+// and a butterfly of three shuffles, always in the same order. The state lies column by column
+// ([.., column, key channel]): a warp reads and writes whole rows of it with 16-byte accesses.
+// q, k and the decays of SCAN_TOKENS tokens at a time stand in shared memory (slices padded by
+// four floats against bank conflicts); the next tokens' values are fetched into registers
+// while these are worked on.
+//
+// MODE 0, gated delta rule. in_a = qkv [rows, lda]: unit q (qk_heads x D), unit k, v (heads x Dv)
+// from conv_unit_kernel; in_b [rows, ldb]: beta before the sigmoid at column b_col + head;
+// in_c [rows, ldc] (heads x D): decay input, g = exp(-exp(a_log[head]) softplus(x + dt_bias)).
+// state [slots, heads, Dv, D]. out [rows, heads x Dv] = S^T q.
+// MODE 1, matrix memory. in_a = proj [rows, lda] with q at q_col (heads x D), k at k_col, v at
+// v_col (heads x Dv), gate inputs at i_col + head and f_col + head (before bias and cap).
+// state [slots, heads, Dv + 1, D] (column Dv is n), state_m [slots, heads, Dv + 1] (m, one copy
+// per column, so that no thread reads what another writes). out [rows, heads, Dv + 2]: S^T q per
+// column, then n . q, then m after the token.
+#define SCAN_TOKENS 8
+#define SCAN_COLS 16
+
+struct ScanParams {
+    const float* in_a; long lda;
+    const float* in_b; long ldb; int b_col;
+    const float* in_c; long ldc;
+    const float* vec_a;           // a_log [heads]            | input-gate bias [heads]
+    const float* vec_b;           // dt_bias [heads x D]      | forget-gate bias [heads]
+    float* state; float* state_m;
+    const int* seq_row0; const int* seq_new; const int* seq_start; const int* seq_slot;
+    float* out;
+    int heads, qk_heads, D, Dv;
+    int q_col, k_col, v_col, i_col, f_col;
+    float cap, q_scale;
+};
+
+__device__ __forceinline__ float slices_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    return v;
+}
+
+template <int DS, int MODE>
+__global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
+    constexpr int DPAD = 8 * DS;                       // key channels a block can take
+    constexpr int SL = DS + 4;                         // floats of a slice in shared memory
+    constexpr int PER = SCAN_TOKENS * DPAD / 128;      // staged values per thread and array
+    __shared__ __align__(16) float sq[SCAN_TOKENS][8 * SL], sk[SCAN_TOKENS][8 * SL], sg[MODE == 0 ? SCAN_TOKENS : 1][8 * SL];
+    __shared__ float sv[SCAN_TOKENS][SCAN_COLS], s1[SCAN_TOKENS], s2[SCAN_TOKENS];
     pdl_wait();
     pdl_launch_dependents();
-    const int s = blockIdx.x, hd = blockIdx.y, g = hd / (heads / qk_heads);
-    const int c = blockIdx.z * blockDim.x + threadIdx.x;
-    const bool live = c < Dv;
-    const int row0 = seq_row0[s], n = seq_new[s];
-    float* st = state + (((size_t)seq_slot[s] * heads + hd) * D) * Dv + (live ? c : 0);
-    float S[DMAX];
-    const bool fresh = seq_start[s] == 0;
+    const int s = blockIdx.x, hd = blockIdx.y;
+    const int D = p.D, Dv = p.Dv, heads = p.heads;
+    const int cols = MODE == 1 ? Dv + 1 : Dv;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int slice = lane & 7;
+    const int c = blockIdx.z * SCAN_COLS + warp * 4 + (lane >> 3);
+    const bool live = c < cols;
+    const int d0 = slice * DS;
+    const int row0 = p.seq_row0[s], n = p.seq_new[s];
+    const bool fresh = p.seq_start[s] == 0;
+    const size_t cell = ((size_t)p.seq_slot[s] * heads + hd) * cols + (live ? c : 0);
+    float* st = p.state + cell * D;
+    const bool vec = (D & 3) == 0;
+    float S[DS];
 #pragma unroll
-    for (int d = 0; d < DMAX; ++d) S[d] = (d < D && live && !fresh) ? st[(size_t)d * Dv] : 0.f;
-    const float a_rate = expf(a_log[hd]);
-    const int vcol = 2 * qk_heads * D + hd * Dv;
-    for (int t0 = 0; t0 < n; t0 += REC_TOKENS) {
-        const int nt = min(REC_TOKENS, n - t0);
-        __syncthreads();
-        for (int i = threadIdx.x; i < nt * D; i += blockDim.x) {
-            const int t = i / D, d = i % D;
-            const size_t r = (size_t)(row0 + t0 + t);
-            sq[t][d] = qkv[r * ldq + g * D + d];
-            sk[t][d] = qkv[r * ldq + (qk_heads + g) * D + d];
-            sg[t][d] = expf(-a_rate * softplus_f(decay_in[r * ldd + hd * D + d] + dt_bias[hd * D + d]));
+    for (int i = 0; i < DS; i += 4) {
+        if (live && !fresh && vec && d0 + i < D) {
+            const float4 t = *reinterpret_cast<const float4*>(st + d0 + i);
+            S[i] = t.x; S[i + 1] = t.y; S[i + 2] = t.z; S[i + 3] = t.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) S[i + j] = (live && !fresh && d0 + i + j < D) ? st[d0 + i + j] : 0.f;
         }
-        for (int i = threadIdx.x; i < nt * (int)blockDim.x; i += blockDim.x) {
-            const int t = i / blockDim.x, cc = blockIdx.z * blockDim.x + i % blockDim.x;
-            sv[t][i % blockDim.x] = cc < Dv ? qkv[(size_t)(row0 + t0 + t) * ldq + vcol + cc] : 0.f;
+    }
+    float m = 0.f;
+    if (MODE == 1 && live && !fresh) m = p.state_m[cell];
+    const int g = MODE == 0 ? hd / (heads / p.qk_heads) : hd;
+    const int qc = MODE == 0 ? g * D : p.q_col + hd * D;
+    const int kc = MODE == 0 ? (p.qk_heads + g) * D : p.k_col + hd * D;
+    const int vc = MODE == 0 ? 2 * p.qk_heads * D + hd * Dv : p.v_col + hd * Dv;
+    const float a_rate = MODE == 0 ? expf(p.vec_a[hd]) : 0.f;
+    // staging: thread -> (token, key channel) of each array, one value of v, and the scalars
+    float rq[PER], rk[PER], rg[MODE == 0 ? PER : 1], rv = 0.f, r1 = 0.f, r2 = 0.f;
+    auto fetch = [&](int t0) {
+        const int nt = min(SCAN_TOKENS, n - t0);
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int idx = threadIdx.x + 128 * e, t = idx / DPAD, d = idx % DPAD;
+            const bool ok = t < nt && d < D;
+            const size_t r = (size_t)(row0 + t0 + (ok ? t : 0));
+            const int dd = ok ? d : 0;
+            rq[e] = p.in_a[r * p.lda + qc + dd];
+            rk[e] = p.in_a[r * p.lda + kc + dd];
+            if (MODE == 0) rg[e] = p.in_c[r * p.ldc + hd * D + dd] + p.vec_b[hd * D + dd];
+            if (!ok) rq[e] = rk[e] = 0.f;              // channels beyond D stay out of every sum
         }
-        if (threadIdx.x < nt) sbeta[threadIdx.x] = sigmoid_f(beta_in[(size_t)(row0 + t0 + threadIdx.x) * ldb + beta_col + hd]);
+        {
+            const int t = threadIdx.x / SCAN_COLS, cc = blockIdx.z * SCAN_COLS + threadIdx.x % SCAN_COLS;
+            const bool ok = t < nt && cc < Dv;
+            rv = p.in_a[(size_t)(row0 + t0 + (ok ? t : 0)) * p.lda + vc + (ok ? cc : 0)];
+            if (!ok) rv = (MODE == 1 && cc == Dv) ? 1.0f : 0.f;          // the column of n has v = 1
+        }
+        if (threadIdx.x < SCAN_TOKENS) {
+            const size_t r = (size_t)(row0 + t0 + (threadIdx.x < nt ? threadIdx.x : 0));
+            if (MODE == 0) r1 = p.in_b[r * p.ldb + p.b_col + hd];
+            else { r1 = p.in_a[r * p.lda + p.i_col + hd]; r2 = p.in_a[r * p.lda + p.f_col + hd]; }
+        }
+    };
+    auto stage = [&]() {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int idx = threadIdx.x + 128 * e, t = idx / DPAD, d = idx % DPAD;
+            const int at = (d / DS) * SL + d % DS;
+            sq[t][at] = MODE == 1 ? rq[e] * p.q_scale : rq[e];
+            sk[t][at] = rk[e];
+            if (MODE == 0) sg[t][at] = expf(-a_rate * softplus_f(rg[e]));
+        }
+        sv[threadIdx.x / SCAN_COLS][threadIdx.x % SCAN_COLS] = rv;
+        if (threadIdx.x < SCAN_TOKENS) {
+            if (MODE == 0) s1[threadIdx.x] = sigmoid_f(r1);
+            else {
+                s1[threadIdx.x] = p.cap * tanhf((r1 + p.vec_a[hd]) / p.cap);
+                s2[threadIdx.x] = logsigmoid_f(p.cap * tanhf((r2 + p.vec_b[hd]) / p.cap));
+            }
+        }
+    };
+    fetch(0);
+    for (int t0 = 0; t0 < n; t0 += SCAN_TOKENS) {
+        const int nt = min(SCAN_TOKENS, n - t0);
+        __syncthreads();                               // the tokens before are done with the staged values
+        stage();
         __syncthreads();
+        if (t0 + SCAN_TOKENS < n) fetch(t0 + SCAN_TOKENS);
         for (int t = 0; t < nt; ++t) {
-            float dot = 0.f;
-#pragma unroll
-            for (int d = 0; d < DMAX; ++d)
-                if (d < D) { S[d] *= sg[t][d]; dot = fmaf(S[d], sk[t][d], dot); }
-            const float u = sbeta[t] * (sv[t][threadIdx.x] - dot);
+            const float* kq = &sk[t][slice * SL];
+            const float* qq = &sq[t][slice * SL];
+            const float vcol = sv[t][warp * 4 + (lane >> 3)];
             float o = 0.f;
+            if (MODE == 0) {
+                const float* gg = &sg[t][slice * SL];
+                float dot = 0.f;
 #pragma unroll
-            for (int d = 0; d < DMAX; ++d)
-                if (d < D) { S[d] = fmaf(sk[t][d], u, S[d]); o = fmaf(S[d], sq[t][d], o); }
-            if (live) out[(size_t)(row0 + t0 + t) * heads * Dv + hd * Dv + c] = o;
+                for (int i = 0; i < DS; i += 4) {
+                    const float4 gv = *reinterpret_cast<const float4*>(gg + i), kv = *reinterpret_cast<const float4*>(kq + i);
+                    S[i] *= gv.x; S[i + 1] *= gv.y; S[i + 2] *= gv.z; S[i + 3] *= gv.w;
+                    dot = fmaf(S[i], kv.x, dot); dot = fmaf(S[i + 1], kv.y, dot);
+                    dot = fmaf(S[i + 2], kv.z, dot); dot = fmaf(S[i + 3], kv.w, dot);
+                }
+                dot = slices_sum(dot);
+                const float u = s1[t] * (vcol - dot);
+#pragma unroll
+                for (int i = 0; i < DS; i += 4) {
+                    const float4 kv = *reinterpret_cast<const float4*>(kq + i), qv = *reinterpret_cast<const float4*>(qq + i);
+                    S[i] = fmaf(kv.x, u, S[i]); S[i + 1] = fmaf(kv.y, u, S[i + 1]);
+                    S[i + 2] = fmaf(kv.z, u, S[i + 2]); S[i + 3] = fmaf(kv.w, u, S[i + 3]);
+                    o = fmaf(S[i], qv.x, o); o = fmaf(S[i + 1], qv.y, o); o = fmaf(S[i + 2], qv.z, o); o = fmaf(S[i + 3], qv.w, o);
+                }
+                o = slices_sum(o);
+                if (live && slice == 0) p.out[(size_t)(row0 + t0 + t) * heads * Dv + hd * Dv + c] = o;
+            } else {
+                const float fm = s2[t] + m;
+                const float m_new = fmaxf(fm, s1[t]);
+                const float a = expf(fm - m_new);
+                const float bv = expf(s1[t] - m_new) * vcol;
+                m = m_new;
+#pragma unroll
+                for (int i = 0; i < DS; i += 4) {
+                    const float4 kv = *reinterpret_cast<const float4*>(kq + i), qv = *reinterpret_cast<const float4*>(qq + i);
+                    S[i] = fmaf(a, S[i], bv * kv.x); S[i + 1] = fmaf(a, S[i + 1], bv * kv.y);
+                    S[i + 2] = fmaf(a, S[i + 2], bv * kv.z); S[i + 3] = fmaf(a, S[i + 3], bv * kv.w);
+                    o = fmaf(S[i], qv.x, o); o = fmaf(S[i + 1], qv.y, o); o = fmaf(S[i + 2], qv.z, o); o = fmaf(S[i + 3], qv.w, o);
+                }
+                o = slices_sum(o);
+                if (live && slice == 0) {
+                    float* orow = p.out + ((size_t)(row0 + t0 + t) * heads + hd) * (Dv + 2);
+                    orow[c] = o;
+                    if (c == Dv) orow[Dv + 1] = m;
+                }
+            }
         }
     }
     if (live) {
 #pragma unroll
-        for (int d = 0; d < DMAX; ++d)
-            if (d < D) st[(size_t)d * Dv] = S[d];
+        for (int i = 0; i < DS; i += 4) {
+            if (vec && d0 + i < D) {
+                *reinterpret_cast<float4*>(st + d0 + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (d0 + i + j < D) st[d0 + i + j] = S[i + j];
+            }
+        }
+        if (MODE == 1 && slice == 0) p.state_m[cell] = m;
     }
+}
+
+template <int MODE>
+static int launch_scan(const ScanParams& p, int n_seqs, cudaStream_t s) {
+    if (n_seqs <= 0) return 0;
+    if (p.D < 1 || p.D > 256 || p.Dv < 1) return CML_ERR_BAD_SIZE;
+    const int cols = MODE == 1 ? p.Dv + 1 : p.Dv;
+    dim3 grid(n_seqs, p.heads, (cols + SCAN_COLS - 1) / SCAN_COLS);
+#define SCAN_CASE(DS_)                                                             \
+    if (p.D <= 8 * DS_) {                                                          \
+        launch_pdl(scan_kernel<DS_, MODE>, grid, dim3(128), 0, s, p);              \
+        return cml_launch_status();                                                \
+    }
+    SCAN_CASE(4) SCAN_CASE(8) SCAN_CASE(16) SCAN_CASE(32)
+#undef SCAN_CASE
+    return CML_ERR_BAD_SIZE;
 }
 
 extern "C" int cml_delta_scan(const float* qkv, long ldq, const float* beta_in, long ldb, int beta_col, const float* decay_in,
                               long ldd, const float* a_log, const float* dt_bias, float* state, const int* seq_row0,
                               const int* seq_new, const int* seq_start, const int* seq_slot, float* out, int n_seqs, int heads,
                               int qk_heads, int D, int Dv, void* stream) {
-    if (n_seqs <= 0) return 0;
-    if (D < 1 || D > 256 || Dv < 1 || heads % qk_heads) return CML_ERR_BAD_SIZE;
-    const int threads = Dv <= 32 ? 32 : (Dv <= 64 ? 64 : 128);
-    dim3 grid(n_seqs, heads, (Dv + threads - 1) / threads);
-    cudaStream_t s = (cudaStream_t)stream;
-#define DS_CASE(DM)                                                                                                        \
-    if (D <= DM) {                                                                                                         \
-        launch_pdl(delta_scan_kernel<DM>, grid, dim3(threads), 0, s, qkv, ldq, beta_in, ldb, beta_col, decay_in, ldd, a_log,  \
-                   dt_bias, state, seq_row0, seq_new, seq_start, seq_slot, out, heads, qk_heads, D, Dv);                   \
-        return cml_launch_status();                                                                                        \
-    }
-    DS_CASE(16) DS_CASE(32) DS_CASE(64) DS_CASE(128) DS_CASE(256)
-#undef DS_CASE
-    return CML_ERR_BAD_SIZE;
-}
-
-// ------------------------------------------------------------------------------------
-// Matrix memory. proj [rows, ld] float holds q at q_col (heads x D), k at k_col, v at v_col
-// (heads x Dv), and the gate inputs at i_col + head and f_col + head (before bias and cap).
-// state [slots, heads, D + 1, Dv + 1]: S with n as column Dv, and m as row D (one copy per
-// column). out [rows, heads, Dv + 2] float: S^T q per column, then n . q, then m after the token.
-template <int DMAX>
-__global__ void __launch_bounds__(128) memory_scan_kernel(
-        const float* __restrict__ proj, long ld, int q_col, int k_col, int v_col, int i_col, int f_col,
-        const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap, float q_scale,
-        float* __restrict__ state, const int* __restrict__ seq_row0, const int* __restrict__ seq_new,
-        const int* __restrict__ seq_start, const int* __restrict__ seq_slot, float* __restrict__ out, int heads, int D,
-        int Dv) {
-    __shared__ float sq[REC_TOKENS][DMAX], sk[REC_TOKENS][DMAX];
-    __shared__ float sv[REC_TOKENS][128], si[REC_TOKENS], sf[REC_TOKENS];
-    pdl_wait();
-    pdl_launch_dependents();
-    const int s = blockIdx.x, hd = blockIdx.y;
-    const int c = blockIdx.z * blockDim.x + threadIdx.x;
-    const int cols = Dv + 1;
-    const bool live = c < cols;
-    const int row0 = seq_row0[s], n = seq_new[s];
-    float* st = state + (((size_t)seq_slot[s] * heads + hd) * (D + 1)) * cols + (live ? c : 0);
-    const bool fresh = seq_start[s] == 0;
-    float S[DMAX];
-#pragma unroll
-    for (int d = 0; d < DMAX; ++d) S[d] = (d < D && live && !fresh) ? st[(size_t)d * cols] : 0.f;
-    float m = (live && !fresh) ? st[(size_t)D * cols] : 0.f;
-    for (int t0 = 0; t0 < n; t0 += REC_TOKENS) {
-        const int nt = min(REC_TOKENS, n - t0);
-        __syncthreads();
-        for (int i = threadIdx.x; i < nt * D; i += blockDim.x) {
-            const int t = i / D, d = i % D;
-            const size_t r = (size_t)(row0 + t0 + t);
-            sq[t][d] = proj[r * ld + q_col + hd * D + d] * q_scale;
-            sk[t][d] = proj[r * ld + k_col + hd * D + d];
-        }
-        for (int i = threadIdx.x; i < nt * (int)blockDim.x; i += blockDim.x) {
-            const int t = i / blockDim.x, cc = blockIdx.z * blockDim.x + i % blockDim.x;
-            sv[t][i % blockDim.x] = cc < Dv ? proj[(size_t)(row0 + t0 + t) * ld + v_col + hd * Dv + cc] : 1.0f;
-        }
-        if (threadIdx.x < nt) {
-            const size_t r = (size_t)(row0 + t0 + threadIdx.x);
-            si[threadIdx.x] = cap * tanhf((proj[r * ld + i_col + hd] + i_bias[hd]) / cap);
-            sf[threadIdx.x] = logsigmoid_f(cap * tanhf((proj[r * ld + f_col + hd] + f_bias[hd]) / cap));
-        }
-        __syncthreads();
-        for (int t = 0; t < nt; ++t) {
-            const float fm = sf[t] + m;
-            const float m_new = fmaxf(fm, si[t]);
-            const float a = expf(fm - m_new);
-            const float bv = expf(si[t] - m_new) * sv[t][threadIdx.x];
-            m = m_new;
-            float o = 0.f;
-#pragma unroll
-            for (int d = 0; d < DMAX; ++d)
-                if (d < D) { S[d] = fmaf(a, S[d], bv * sk[t][d]); o = fmaf(S[d], sq[t][d], o); }
-            if (live) {
-                float* orow = out + ((size_t)(row0 + t0 + t) * heads + hd) * (Dv + 2);
-                orow[c] = o;
-                if (c == Dv) orow[Dv + 1] = m;
-            }
-        }
-    }
-    if (live) {
-#pragma unroll
-        for (int d = 0; d < DMAX; ++d)
-            if (d < D) st[(size_t)d * cols] = S[d];
-        st[(size_t)D * cols] = m;
-    }
+    if (qk_heads < 1 || heads % qk_heads) return CML_ERR_BAD_SIZE;
+    ScanParams p = {};
+    p.in_a = qkv; p.lda = ldq; p.in_b = beta_in; p.ldb = ldb; p.b_col = beta_col; p.in_c = decay_in; p.ldc = ldd;
+    p.vec_a = a_log; p.vec_b = dt_bias; p.state = state; p.state_m = nullptr;
+    p.seq_row0 = seq_row0; p.seq_new = seq_new; p.seq_start = seq_start; p.seq_slot = seq_slot; p.out = out;
+    p.heads = heads; p.qk_heads = qk_heads; p.D = D; p.Dv = Dv;
+    return launch_scan<0>(p, n_seqs, (cudaStream_t)stream);
 }
 
 extern "C" int cml_memory_scan(const float* proj, long ld, int q_col, int k_col, int v_col, int i_col, int f_col,
                                const float* i_bias, const float* f_bias, float cap, float q_scale, float* state,
-                               const int* seq_row0, const int* seq_new, const int* seq_start, const int* seq_slot, float* out,
-                               int n_seqs, int heads, int D, int Dv, void* stream) {
-    if (n_seqs <= 0) return 0;
-    if (D < 1 || D > 256 || Dv < 1) return CML_ERR_BAD_SIZE;
-    const int cols = Dv + 1;
-    const int threads = cols <= 32 ? 32 : (cols <= 64 ? 64 : 128);
-    dim3 grid(n_seqs, heads, (cols + threads - 1) / threads);
-    cudaStream_t s = (cudaStream_t)stream;
-#define MS_CASE(DM)                                                                                                        \
-    if (D <= DM) {                                                                                                         \
-        launch_pdl(memory_scan_kernel<DM>, grid, dim3(threads), 0, s, proj, ld, q_col, k_col, v_col, i_col, f_col, i_bias,    \
-                   f_bias, cap, q_scale, state, seq_row0, seq_new, seq_start, seq_slot, out, heads, D, Dv);                \
-        return cml_launch_status();                                                                                        \
-    }
-    MS_CASE(16) MS_CASE(32) MS_CASE(64) MS_CASE(128) MS_CASE(256)
-#undef MS_CASE
-    return CML_ERR_BAD_SIZE;
+                               float* state_m, const int* seq_row0, const int* seq_new, const int* seq_start,
+                               const int* seq_slot, float* out, int n_seqs, int heads, int D, int Dv, void* stream) {
+    ScanParams p = {};
+    p.in_a = proj; p.lda = ld; p.vec_a = i_bias; p.vec_b = f_bias; p.state = state; p.state_m = state_m;
+    p.seq_row0 = seq_row0; p.seq_new = seq_new; p.seq_start = seq_start; p.seq_slot = seq_slot; p.out = out;
+    p.heads = heads; p.qk_heads = heads; p.D = D; p.Dv = Dv;
+    p.q_col = q_col; p.k_col = k_col; p.v_col = v_col; p.i_col = i_col; p.f_col = f_col; p.cap = cap; p.q_scale = q_scale;
+    return launch_scan<1>(p, n_seqs, (cudaStream_t)stream);
 }
 
 // ------------------------------------------------------------------------------------

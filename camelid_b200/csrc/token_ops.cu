@@ -253,9 +253,22 @@ __global__ void norm_combine_kernel(CombineBranches br, float* __restrict__ resi
     for (int b = 0; b < br.n; ++b) {
         const float* y = br.y[b] + (size_t)r * hidden;
         float ss = 0.f;
+        const int ns = br.splits[b];
+        const size_t stride = br.split_stride[b];
         for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-            float v = y[c];
-            for (int s = 1; s < br.splits[b]; ++s) v += y[(size_t)s * br.split_stride[b] + c];
+            // eight splits at a time: the loads are unconditional (of a valid place) and all in flight
+            // before the first add; the adds stay in split order
+            float v = 0.f;
+            for (int s0 = 0; s0 < ns; s0 += 8) {
+                float t[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float tv = y[(size_t)min(s0 + i, ns - 1) * stride + c];
+                    t[i] = s0 + i < ns ? tv : 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v += t[i];
+            }
             rowbuf[c] = v;
             ss = fmaf(v, v, ss);
         }
@@ -281,7 +294,7 @@ extern "C" int cml_norm_combine(const float* const* y, const void* const* w, con
         br.split_stride[b] = b < n_branches ? split_stride[b] : 0;
     }
     cudaStream_t s = (cudaStream_t)stream;
-    const int block = hidden >= 1024 ? 256 : 128;
+    const int block = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
     if (w_dtype == CML_DTYPE_F32) {

@@ -86,8 +86,9 @@ def plan_for_model(model, max_tokens: int = 0, max_slots: int | None = None, ste
                 cache += n_slots * _numel(spec.shape) * _elem(_STATE_DTYPES[spec.dtype])
     rows = int(step_tokens) if step_tokens else min(max(int(max_tokens), 1), 2048)
     hidden = model.hidden_size
-    widest = max([hidden] + [_numel(s.shape) // max(1, s.shape[-1]) for s in specs.values() if len(s.shape) == 2
-                             and s.shape[0] != model.vocab_size])
+    tables = set(model.embedding.tensor_specs())          # of a table a step reads rows; it is no activation's width
+    widest = max([hidden] + [_numel(s.shape) // max(1, s.shape[-1]) for n, s in specs.items() if len(s.shape) == 2
+                             and s.shape[0] != model.vocab_size and n not in tables])
     # one step: the float32 residual stream, the normed rows, q/k/v, the attention output and the
     # widest activation in the compute type; float32 split sums of one product (up to 8 splits of
     # the rows that decode paths take, 4 of a wide step); float32 logits of one row per sequence

@@ -81,8 +81,9 @@ class MatrixMemory(Part):
         self.i_bias, self.f_bias, self.norm_w = f32("i.b"), f32("f.b"), f32("norm")
 
     def cache_spec(self):
-        # S with n as one more column, m as one more row
-        return StateSpec((self.num_heads, self.key_dim + 1, self.value_dim + 1), "float32", "memory")
+        # S column by column with n as one more column; the running maximum, one copy per column
+        return [StateSpec((self.num_heads, self.value_dim + 1, self.key_dim), "float32", "memory"),
+                StateSpec((self.num_heads, self.value_dim + 1), "float32", "maximum")]
 
     def read_out(self, ctx, x):
         n = ctx.n_rows
@@ -90,7 +91,7 @@ class MatrixMemory(Part):
         linear.linear(ctx, x, self.w_in, proj, linear.STORE_F32)
         raw = ctx.buffer("mm_raw", (n, self.num_heads, self.value_dim + 2), torch.float32)
         ops.memory_scan(proj, self.cols, self.i_bias, self.f_bias, self.gate_cap, self.key_dim ** -0.5, ctx.state("memory"),
-                        ctx.seq_row0, ctx.seq_new, ctx.seq_start, ctx.seq_slot, raw, ctx.n_seqs, self.num_heads,
+                        ctx.state("maximum"), ctx.seq_row0, ctx.seq_new, ctx.seq_start, ctx.seq_slot, raw, ctx.n_seqs, self.num_heads,
                         self.key_dim, self.value_dim)
         out = ctx.buffer("mm_out", (n, self.v_width))
         ops.head_norm_gate(raw, True, self.norm_w, True, proj, self.gate_col, out, self.num_heads, self.value_dim, self.eps)
@@ -166,7 +167,7 @@ class ChannelDelta(Part):
         self.a_log, self.dt_bias, self.norm_w = f32("A_log"), f32("dt_bias"), f32("norm")
 
     def cache_spec(self):
-        return [StateSpec((self.num_heads, self.key_dim, self.value_dim), "float32", "memory"),
+        return [StateSpec((self.num_heads, self.value_dim, self.key_dim), "float32", "memory"),
                 StateSpec((max(self.taps - 1, 1), self.channels), "float32", "conv")]
 
     def read_out(self, ctx, x):

@@ -46,10 +46,10 @@ def test_every_pass_has_its_own_cache_and_state():
     assert len(needs) == len(m.schedule) + 1                      # the embedding's previous token comes last
     assert needs[-1] == [StateSpec((1,), "int32", "previous_token")]
     first = needs[0]
-    assert KVSpec(2, 24, 9, 40) in first and StateSpec((3, 21, 25), "float32", "memory") in first
+    assert KVSpec(2, 24, 9, 40) in first and StateSpec((3, 25, 20), "float32", "memory") in first and StateSpec((3, 25), "float32", "maximum") in first
     assert StateSpec((1, 64), "float32", "shift") in first
     assert needs[1] == needs[3] == needs[5]                       # the same layer, three passes: three entries
-    assert StateSpec((4, 12, 20), "float32", "memory") in needs[1] and StateSpec((2, 2 * 24 + 80), "float32", "conv") in needs[1]
+    assert StateSpec((4, 20, 12), "float32", "memory") in needs[1] and StateSpec((2, 2 * 24 + 80), "float32", "conv") in needs[1]
     plan = m.memory_plan(256, 4)
     assert plan.cache > 0 and plan.weights == sum(math.prod(s.shape) * 4 for s in m.tensor_specs().values())
 

@@ -316,7 +316,7 @@ def test_scan_kernels_keep_a_far_key(cuda, cut):
     ref = pf.delta_core(q, k, v, torch.sigmoid(beta_in.double()), decay).reshape(T, H * Dv)
     assert float(ref[290].abs().max()) > 0.05
     qkv = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], 1).float().to(cuda)
-    state = torch.full((2, H, D, Dv), 5.0, device=cuda)                # stale: a sequence that starts here reads none of it
+    state = torch.full((2, H, Dv, D), 5.0, device=cuda)                # stale: a sequence that starts here reads none of it
     got = []
     for at, n in portions(T, cut):
         a = arrays(cuda, [at], [n])
@@ -338,12 +338,13 @@ def test_scan_kernels_keep_a_far_key(cuda, cut):
     ref = pf.matrix_memory_core(q.double() * D ** -0.5, k.double(), v.double(), gi, gf)
     proj = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1), gi_in, gf_in], 1).to(cuda)
     cols = (0, H * D, 2 * H * D, 2 * H * D + H * Dv, 2 * H * D + H * Dv + H)
-    state = torch.full((2, H, D + 1, Dv + 1), 5.0, device=cuda)
+    state = torch.full((2, H, Dv + 1, D), 5.0, device=cuda)
+    state_m = torch.full((2, H, Dv + 1), 5.0, device=cuda)
     got = []
     for at, n in portions(T, cut):
         a = arrays(cuda, [at], [n])
         raw = torch.empty(n, H, Dv + 2, device=cuda)
-        ops.memory_scan(proj[at:at + n], cols, bi.to(cuda), bf.to(cuda), cap, D ** -0.5, state, a["seq_row0"], a["seq_new"],
+        ops.memory_scan(proj[at:at + n], cols, bi.to(cuda), bf.to(cuda), cap, D ** -0.5, state, state_m, a["seq_row0"], a["seq_new"],
                         a["seq_start"], a["seq_slot"], raw, 1, H, D, Dv)
         got.append(raw.cpu())
     raw = torch.cat(got).double()
