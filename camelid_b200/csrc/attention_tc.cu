@@ -33,6 +33,8 @@ struct AtParams {
     AttnParams a;
     int* err;
     int n_tiles;
+    const float* r1;        // per head, or null: the score loses r1 ln(1 + r2 (i - j)), a penalty on distance
+    const float* r2;
 };
 
 __device__ __forceinline__ uint32_t at_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -361,6 +363,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                     s[c] = in ? s[c] : -CUDART_INF_F;
                 }
             }
+            if (ap.r1 != nullptr) {
+                // scores are kept raw (before the scale): the penalty is divided by it. Distances of keys that
+                // are masked anyway are clamped to zero, so that the logarithm stays finite there.
+                const float b1 = valid ? ap.r1[head] * 0.6931471805599453f / p.scale : 0.f;
+                const float b2 = valid ? ap.r2[head] : 0.f;
+                const float d0 = (float)(pos - key0);
+#pragma unroll
+                for (int c = 0; c < AT_KEYS; ++c) s[c] -= b1 * __log2f(fmaf(b2, fmaxf(d0 - (float)c, 0.f), 1.0f));
+            }
             {   // eight independent chains of three-input maxima, not one chain of 64
                 float mx8[8];
 #pragma unroll
@@ -512,12 +523,13 @@ static int at_launch(const CUtensorMap& mk, const CUtensorMap& mv, AtParams ap, 
 
 // Tiles of rows_per_tile tokens with rows_per_tile * heads_per_cta <= 128; n_pages: pages of the pool.
 // q rows must be 16-byte aligned (q_stride and head_dim multiples of 8), the output likewise.
-extern "C" int cml_attn_prefill_tc(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                   const void* v_pages, long n_pages, const int* block_table, int max_blocks,
-                                   const int* tile_seq, const int* tile_q0, int n_tiles, const int* seq_row0,
-                                   const int* seq_start, const int* seq_new, int n_heads, int n_kv_heads, int head_dim,
-                                   int rows_per_tile, int heads_per_cta, int head_chunks, int window, float scale,
-                                   int* err, void* stream) {
+// r1, r2 (float [n_heads] each, or both null): score(i, j) = (q . k) scale - r1[head] ln(1 + r2[head] (i - j)).
+extern "C" int cml_attn_prefill_tc_penalty(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                           const void* v_pages, long n_pages, const int* block_table, int max_blocks,
+                                           const int* tile_seq, const int* tile_q0, int n_tiles, const int* seq_row0,
+                                           const int* seq_start, const int* seq_new, int n_heads, int n_kv_heads,
+                                           int head_dim, int rows_per_tile, int heads_per_cta, int head_chunks, int window,
+                                           float scale, const float* r1, const float* r2, int* err, void* stream) {
     if (n_tiles <= 0) return 0;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return CML_ERR_BAD_SIZE;
     if (rows_per_tile < 1 || heads_per_cta < 1 || rows_per_tile * heads_per_cta > AT_ROWS) return CML_ERR_BAD_SIZE;
@@ -539,7 +551,20 @@ extern "C" int cml_attn_prefill_tc(const void* q, int q_stride, void* out, int o
     p.rows_per_tile = rows_per_tile; p.heads_per_cta = heads_per_cta; p.head_chunks = head_chunks;
     p.n_splits = 1; p.window = window; p.scale = scale; p.partial = nullptr; p.tickets = nullptr;
     ap.err = err;
+    ap.r1 = (r1 && r2) ? r1 : nullptr;
+    ap.r2 = (r1 && r2) ? r2 : nullptr;
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 64) return at_launch<64>(mk, mv, ap, n_tiles, s);
     return at_launch<128>(mk, mv, ap, n_tiles, s);
+}
+
+extern "C" int cml_attn_prefill_tc(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                   const void* v_pages, long n_pages, const int* block_table, int max_blocks,
+                                   const int* tile_seq, const int* tile_q0, int n_tiles, const int* seq_row0,
+                                   const int* seq_start, const int* seq_new, int n_heads, int n_kv_heads, int head_dim,
+                                   int rows_per_tile, int heads_per_cta, int head_chunks, int window, float scale,
+                                   int* err, void* stream) {
+    return cml_attn_prefill_tc_penalty(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, max_blocks,
+                                       tile_seq, tile_q0, n_tiles, seq_row0, seq_start, seq_new, n_heads, n_kv_heads, head_dim,
+                                       rows_per_tile, heads_per_cta, head_chunks, window, scale, nullptr, nullptr, err, stream);
 }

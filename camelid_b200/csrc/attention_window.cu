@@ -155,6 +155,7 @@ __global__ void window_attention_kernel(const T* __restrict__ q, const T* __rest
                 const T* kr = k_pages + (((size_t)page * kv_heads + g) * CML_PAGE + j % CML_PAGE) * D;
                 float dot = 0.f;
                 if (pieces) {
+#pragma unroll 8
                     for (int c = 0; c < D; c += Piece<T>::N) {
                         float kf[Piece<T>::N];
                         Piece<T>::load(kr + c, kf);
@@ -176,6 +177,7 @@ __global__ void window_attention_kernel(const T* __restrict__ q, const T* __rest
 #pragma unroll
         for (int e = 0; e < AW_MAX_VREGS; ++e) acc[e] *= fix;
         const int nk = min(32, j_end - j0);
+#pragma unroll 4
         for (int t = 0; t < nk; ++t) {
             const float pt = __shfl_sync(0xffffffffu, p, t);
             const int pg = __shfl_sync(0xffffffffu, page, t);

@@ -54,6 +54,10 @@ _SIGNATURES = {
     ("attention_tc", "cml_attn_prefill_tc"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p,
                                               c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    ("attention_tc", "cml_attn_prefill_tc_penalty"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p,
+                                                      c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                      c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+                                                      c_void_p, c_void_p],
     ("gemm_simt", "cml_gemm_tn_simt"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_void_p, c_void_p, c_void_p],
     ("gemm_simt", "cml_gemv_f32_scratch_bytes"): [c_int, c_int, c_int, c_int],
@@ -84,6 +88,8 @@ _SIGNATURES = {
                                        c_void_p, c_int, c_int, c_void_p],
     ("token_ops", "cml_add_rows_vec"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     ("token_ops", "cml_gelu_tanh"): [c_void_p, c_int, c_long, c_void_p],
+    ("token_ops", "cml_act_from_partials"): [c_void_p, c_int, c_long, c_void_p, c_int, c_long, c_int, c_void_p],
+    ("token_ops", "cml_gate_rows"): [c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p],
     ("token_ops", "cml_softcap"): [c_void_p, c_long, c_float, c_void_p],
     ("token_ops", "cml_norm_combine"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_float,
                                         c_float, c_void_p],
@@ -367,6 +373,24 @@ def gelu_tanh_(x: torch.Tensor):
     _dev(x)
     assert x.is_contiguous()
     _check(_fn("token_ops", "cml_gelu_tanh")(_p(x), dtype_code(x.dtype), x.numel(), _stream()), "gelu_tanh")
+
+
+def act_from_partials(part: torch.Tensor, out: torch.Tensor, gelu: bool):
+    """out = act(sum over splits of part) in the compute type; part float32 [splits, rows, n], act GELU (tanh form) or none."""
+    _dev(part, out)
+    assert part.dtype == torch.float32 and part.dim() == 3 and part.is_contiguous() and out.is_contiguous()
+    assert tuple(out.shape) == tuple(part.shape[1:])
+    _check(_fn("token_ops", "cml_act_from_partials")(_p(part), part.shape[0], part.stride(0), _p(out), dtype_code(out.dtype),
+                                                     out.numel(), 1 if gelu else 0, _stream()), "act_from_partials")
+
+
+def gate_rows_(x: torch.Tensor, gate: torch.Tensor, gate_col: int):
+    """x[r, c] *= sigmoid(gate[r, gate_col + c]) in place; gate float32."""
+    _dev(x, gate)
+    rows, width = x.shape
+    assert x.is_contiguous() and gate.dtype == torch.float32 and gate.stride(1) == 1 and gate_col + width <= gate.shape[1]
+    _check(_fn("token_ops", "cml_gate_rows")(_p(x), dtype_code(x.dtype), _p(gate), gate.stride(0), gate_col, rows, width,
+                                             _stream()), "gate_rows")
 
 
 def softcap_(x: torch.Tensor, cap: float):
@@ -774,16 +798,21 @@ def attn_tc_usable(q: torch.Tensor, out: torch.Tensor, head_dim: int) -> bool:
 
 
 def attn_prefill_tc(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_tiles, seq_row0, seq_start, seq_new,
-                    n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, window, scale, err):
-    """bfloat16 prefill attention of packed query rows over the paged cache with tcgen05.mma."""
-    _dev(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, seq_row0, seq_start, seq_new, err)
+                    n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, window, scale, err,
+                    r1=None, r2=None):
+    """bfloat16 prefill attention of packed query rows over the paged cache with tcgen05.mma. ``r1``, ``r2``
+    (float32 [heads]): the score of key j for query i loses r1 ln(1 + r2 (i - j))."""
+    _dev(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, seq_row0, seq_start, seq_new, err, r1, r2)
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == torch.bfloat16
     assert k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim) and k_pages.is_contiguous() and v_pages.is_contiguous()
-    _check(_fn("attention_tc", "cml_attn_prefill_tc")(
+    assert v_pages.shape == k_pages.shape
+    if r1 is not None:
+        assert r1.dtype == torch.float32 and r2.dtype == torch.float32 and r1.numel() == n_heads and r2.numel() == n_heads
+    _check(_fn("attention_tc", "cml_attn_prefill_tc_penalty")(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), k_pages.shape[0], _p(block_table),
         block_table.shape[1], _p(tile_seq), _p(tile_q0), n_tiles, _p(seq_row0), _p(seq_start), _p(seq_new), n_heads,
-        n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, int(window or 0), float(scale), _p(err),
-        _stream()), "attn_prefill_tc")
+        n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, int(window or 0), float(scale), _p(r1), _p(r2),
+        _p(err), _stream()), "attn_prefill_tc")
 
 
 def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, group: int = 0, err=None):

@@ -215,6 +215,68 @@ extern "C" int cml_gelu_tanh(void* x, int dtype, long n, void* stream) {
     return cml_launch_status();
 }
 
+// out[i] = act(sum over splits of part[split][i]) in the compute type: the split sums of a product of few
+// rows, added in split order, through GELU (act 1) or as they are (act 0).
+template <typename T>
+__global__ void act_from_partials_kernel(const float* __restrict__ part, int n_splits, size_t stride, T* __restrict__ out,
+                                         long n, int act) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        float v = 0.f;
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {
+            float t[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float tv = part[(size_t)min(s0 + k, n_splits - 1) * stride + i];
+                t[k] = s0 + k < n_splits ? tv : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v += t[k];
+        }
+        out[i] = from_f32<T>(act == 1 ? gelu_tanh_f(v) : v);
+    }
+}
+
+extern "C" int cml_act_from_partials(const float* part, int n_splits, long stride, void* out, int dtype, long n, int act,
+                                     void* stream) {
+    if (n <= 0) return 0;
+    if (n_splits < 1) return CML_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int grid = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+    if (dtype == CML_DTYPE_F32)
+        launch_pdl(act_from_partials_kernel<float>, dim3(grid), dim3(256), 0, s, part, n_splits, (size_t)stride, (float*)out, n, act);
+    else if (dtype == CML_DTYPE_BF16)
+        launch_pdl(act_from_partials_kernel<bf16>, dim3(grid), dim3(256), 0, s, part, n_splits, (size_t)stride, (bf16*)out, n, act);
+    else
+        return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}
+
+// x[r, c] *= sigmoid(gate[r, gate_col + c]) in place (x in the compute type, gate float).
+template <typename T>
+__global__ void gate_rows_kernel(T* __restrict__ x, const float* __restrict__ gate, long ldg, int gate_col, long n, int width) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const long r = i / width;
+        const int c = (int)(i - r * width);
+        const float g = gate[r * ldg + gate_col + c];
+        x[i] = from_f32<T>(to_f32(x[i]) / (1.0f + expf(-g)));
+    }
+}
+
+extern "C" int cml_gate_rows(void* x, int dtype, const float* gate, long ldg, int gate_col, int rows, int width, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long n = (long)rows * width;
+    const int grid = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+    if (dtype == CML_DTYPE_F32) launch_pdl(gate_rows_kernel<float>, dim3(grid), dim3(256), 0, s, (float*)x, gate, ldg, gate_col, n, width);
+    else if (dtype == CML_DTYPE_BF16) launch_pdl(gate_rows_kernel<bf16>, dim3(grid), dim3(256), 0, s, (bf16*)x, gate, ldg, gate_col, n, width);
+    else return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}
+
 // x = cap * tanh(x / cap) in place (float logits).
 __global__ void softcap_kernel(float* __restrict__ x, long n, float cap) {
     pdl_wait();

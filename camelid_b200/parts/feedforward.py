@@ -71,6 +71,5 @@ class DenseGelu(Part):
 
     def forward(self, ctx, x, residual):
         act = ctx.buffer("ffn_act", (ctx.n_rows, self.intermediate_size))
-        linear.linear(ctx, x, self.w_up, act, linear.STORE)
-        ops.gelu_tanh_(act)
+        linear.product_act(ctx, x, self.w_up, act, "up_partial", gelu=True)
         linear.add_into_residual(ctx, act, self.w_down, residual, "down_partial")

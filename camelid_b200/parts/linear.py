@@ -163,6 +163,31 @@ def partial_sums(ctx, x: torch.Tensor, w: torch.Tensor, name: str, row_scale=Non
     return part
 
 
+def product_rows_f32(ctx, x: torch.Tensor, w: torch.Tensor, name: str) -> torch.Tensor:
+    """x @ w.T as complete float32 rows [rows, out] in the step's buffer ``name``. Where the step's size
+    splits K (few rows: every SM streams weights), the split sums are added into the first of them."""
+    part = partial_sums(ctx, x, w, name)
+    if part is None:
+        out = ctx.buffer(name, (x.shape[0], w.shape[0]), torch.float32)
+        linear(ctx, x, w, out, STORE_F32)
+        return out
+    if part.shape[0] > 1:
+        ops.add_partials(part[0], part[1:])
+    return part[0]
+
+
+def product_act(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, name: str, gelu: bool) -> None:
+    """out = act(x @ w.T) in the compute type, act GELU (tanh form) or none. Few rows: split sums through
+    one kernel that adds them and applies the activation; many rows: the product's store, then the activation."""
+    part = partial_sums(ctx, x, w, name)
+    if part is not None:
+        ops.act_from_partials(part, out, gelu)
+        return
+    linear(ctx, x, w, out, STORE)
+    if gelu:
+        ops.gelu_tanh_(out)
+
+
 def product_f32(ctx, x: torch.Tensor, w: torch.Tensor, name: str) -> torch.Tensor:
     """x @ w.T in float32 in the step's buffer ``name``: split sums [splits, rows, out] where the
     step's size splits K (the reader adds them in split order), else [rows, out]."""

@@ -87,8 +87,7 @@ class MatrixMemory(Part):
 
     def read_out(self, ctx, x):
         n = ctx.n_rows
-        proj = ctx.buffer("mm_proj", (n, self.w_in.shape[0]), torch.float32)
-        linear.linear(ctx, x, self.w_in, proj, linear.STORE_F32)
+        proj = linear.product_rows_f32(ctx, x, self.w_in, "mm_proj")
         raw = ctx.buffer("mm_raw", (n, self.num_heads, self.value_dim + 2), torch.float32)
         ops.memory_scan(proj, self.cols, self.i_bias, self.f_bias, self.gate_cap, self.key_dim ** -0.5, ctx.state("memory"),
                         ctx.state("maximum"), ctx.seq_row0, ctx.seq_new, ctx.seq_start, ctx.seq_slot, raw, ctx.n_seqs, self.num_heads,
@@ -172,12 +171,10 @@ class ChannelDelta(Part):
 
     def read_out(self, ctx, x):
         n = ctx.n_rows
-        proj = ctx.buffer("cd_proj", (n, self.w_in.shape[0]), torch.float32)
-        linear.linear(ctx, x, self.w_in, proj, linear.STORE_F32)
+        proj = linear.product_rows_f32(ctx, x, self.w_in, "cd_proj")
         low = ctx.buffer("cd_low", (n, self.w_low.shape[0]))
-        linear.linear(ctx, x, self.w_low, low, linear.STORE)
-        high = ctx.buffer("cd_high", (n, self.w_high.shape[0]), torch.float32)      # decay inputs, then gate inputs
-        linear.linear(ctx, low, self.w_high, high, linear.STORE_F32)
+        linear.product_act(ctx, x, self.w_low, low, "cd_low_partial", gelu=False)
+        high = linear.product_rows_f32(ctx, low, self.w_high, "cd_high")          # decay inputs, then gate inputs
         conv_state = ctx.state("conv")
         qkv = ctx.buffer("cd_qkv", (n, self.channels), torch.float32)
         ops.conv_unit(proj, self.conv_w, conv_state, ctx.row_seq, ctx.row_pos, ctx.seq_row0, ctx.seq_slot, qkv,

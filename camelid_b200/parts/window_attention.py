@@ -84,17 +84,32 @@ class WindowAttention(Part):
         return KVSpec(self.num_kv_heads, self.head_dim, self.window,
                       self.value_dim if self.value_dim != self.head_dim else None)
 
+    def query_tile_sizes(self):
+        if self.value_dim == self.head_dim and self.head_dim in (64, 128):
+            return [ops.attn_tc_tiling(self.num_heads, self.num_kv_heads)[0]]
+        return []
+
     def attend(self, ctx, x):
         """The gated heads [rows, heads * value_dim] in the compute type: the input of the output projection."""
         n = ctx.n_rows
         group, k_pages, v_pages = ctx.kv()
         table = ctx.block_table(group)
-        proj = ctx.buffer("wa_proj", (n, self.w_in.shape[0]), torch.float32)
-        linear.linear(ctx, x, self.w_in, proj, linear.STORE_F32)
+        proj = linear.product_rows_f32(ctx, x, self.w_in, "wa_proj")
         q = ctx.buffer("wa_q", (n, self.q_width))
         ops.qk_norm_kv_write(proj, self.q_w, self.k_w, self.eps, ctx.row_seq, ctx.row_pos, table, q, k_pages, v_pages,
                              self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim)
         out = ctx.buffer("wa_out", (n, self.o_width))
+        # prompts in bfloat16 with keys and values of 64 or 128 channels: the tcgen05 kernel of the library's
+        # attention (scores and softmax in float there too), then the gate; everything else on the kernel below
+        if not ctx.decode and self.value_dim == self.head_dim and ops.attn_tc_usable(q, out, self.head_dim):
+            rows, hpc, chunks = ops.attn_tc_tiling(self.num_heads, self.num_kv_heads)
+            tile_seq, tile_q0, n_tiles = ctx.query_tiles(rows)
+            ops.attn_prefill_tc(q, out, k_pages, v_pages, table, tile_seq, tile_q0, n_tiles, ctx.seq_row0, ctx.seq_start,
+                                ctx.seq_new, self.num_heads, self.num_kv_heads, self.head_dim, rows, hpc, chunks,
+                                self.window or 0, self.scale, linear._err_word(q.device), self.r1, self.r2)
+            if self.output_gate:
+                ops.gate_rows_(out, proj, self.gate_col)
+            return out
         ops.window_attention(q, k_pages, v_pages, table, ctx.row_seq, ctx.row_pos, self.r1, self.r2,
                              proj if self.output_gate else None, self.gate_col, out, self.num_heads, self.num_kv_heads,
                              self.head_dim, self.value_dim, self.window or 0, self.scale)

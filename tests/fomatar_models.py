@@ -51,10 +51,12 @@ FROM_START = config(44, 61, [
     parallel((8, 12, 2, 1, 4, 0.35), (12, 8, 2, 5.0)),
     delta(8, 12, 2, 2, 4, mlp=36),
 ], loop=(0, 2, 2), bigram=(7, 5, 3))
-# wide heads: 160 value channels (two blocks of columns per head in the scans), key size 72 (the 128-register form)
+# wide heads: 160 value channels (ten blocks of columns per head in the scans), key size 72; attention heads
+# of 64 channels for keys and values alike (in bfloat16 the tensor-core kernel for prompts), 3 query heads per
+# kv head, a window of 130 over pages of 64
 WIDE = config(96, 83, [
     delta(72, 160, 2, 1, 4),
-    parallel((64, 128, 2, 1, 130, 0.125), (72, 140, 1, 15.0), mlp=128),
+    parallel((64, 64, 3, 1, 130, 0.125), (72, 140, 1, 15.0), mlp=128),
 ], loop=None)
 CONFIGS = {"mixed": MIXED, "plain": PLAIN, "from_start": FROM_START, "wide": WIDE}
 
