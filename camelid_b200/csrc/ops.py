@@ -86,6 +86,8 @@ _SIGNATURES = {
                                           c_void_p, c_int, c_void_p],
     ("token_ops", "cml_token_shift"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_int, c_int, c_void_p],
+    ("token_ops", "cml_rmsnorm_shift"): [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_int, c_int, c_int, c_float, c_void_p, c_int, c_long, c_void_p],
     ("token_ops", "cml_add_rows_vec"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     ("token_ops", "cml_gelu_tanh"): [c_void_p, c_int, c_long, c_void_p],
     ("token_ops", "cml_act_from_partials"): [c_void_p, c_int, c_long, c_void_p, c_int, c_long, c_int, c_void_p],
@@ -93,7 +95,7 @@ _SIGNATURES = {
     ("token_ops", "cml_softcap"): [c_void_p, c_long, c_float, c_void_p],
     ("token_ops", "cml_norm_combine"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_float,
                                         c_float, c_void_p],
-    ("recurrence", "cml_conv_unit"): [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+    ("recurrence", "cml_conv_unit"): [c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     ("recurrence", "cml_delta_scan"): [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_long, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -357,6 +359,24 @@ def token_shift(h: torch.Tensor, mix: torch.Tensor, state: torch.Tensor, row_seq
                                                _stream()), "token_shift")
 
 
+def rmsnorm_shift(x: torch.Tensor, weight: torch.Tensor, eps: float, mix: torch.Tensor, state: torch.Tensor, row_seq, row_pos,
+                  seq_slot, out: torch.Tensor, partial: torch.Tensor | None = None):
+    """One-token steps: ``rmsnorm`` (with the pending split sums added and written back), ``token_shift`` and
+    the keeping of the normed row in one launch; every row is the one new row of its sequence."""
+    _dev(x, weight, mix, state, row_seq, row_pos, seq_slot, out, partial)
+    rows, hidden = out.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.shape == (rows, hidden) and out.is_contiguous()
+    assert mix.dtype == torch.float32 and mix.numel() == hidden and weight.numel() == hidden
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[-1] == hidden
+    n_splits, stride = 0, 0
+    if partial is not None:
+        assert partial.dtype == torch.float32 and partial.is_contiguous() and partial.shape[1:] == x.shape
+        n_splits, stride = partial.shape[0], partial.stride(0)
+    _check(_fn("token_ops", "cml_rmsnorm_shift")(_p(x), _p(weight), dtype_code(weight.dtype), _p(mix), _p(state), _p(row_seq),
+                                                 _p(row_pos), _p(seq_slot), _p(out), dtype_code(out.dtype), rows, hidden,
+                                                 float(eps), _p(partial), n_splits, stride, _stream()), "rmsnorm_shift")
+
+
 def add_rows_vec(h: torch.Tensor, base, vec: torch.Tensor):
     """h[r] += (base[r] if given) + vec, float32 rows in place."""
     _dev(h, base, vec)
@@ -422,10 +442,13 @@ def norm_combine(branches: list, residual: torch.Tensor, eps: float, coef: float
 # recurrent mixers with a matrix state per head
 
 def conv_unit(proj: torch.Tensor, conv_w: torch.Tensor, state: torch.Tensor, row_seq, row_pos, seq_row0, seq_slot,
-              out: torch.Tensor, qk_heads: int, heads: int, key_dim: int, value_dim: int, q_scale: float):
+              out: torch.Tensor, qk_heads: int, heads: int, key_dim: int, value_dim: int, q_scale: float,
+              update_state: bool = False):
     """Short causal convolution + SiLU over the q, k, v channels at the start of ``proj``'s columns
     (float32), then unit norm of q and k per head, q times ``q_scale``. ``conv_w`` float32
-    [channels, taps]; ``state`` float32 [slots, taps - 1, channels]: the inputs before the step."""
+    [channels, taps]; ``state`` float32 [slots, taps - 1, channels]: the inputs before the step. With
+    ``update_state`` (only where every sequence brings exactly one row) the state moves on by that row here;
+    otherwise ``keep_last_rows`` does that afterwards."""
     _dev(proj, conv_w, state, row_seq, row_pos, seq_row0, seq_slot, out)
     channels, taps = conv_w.shape
     rows = out.shape[0]
@@ -433,7 +456,7 @@ def conv_unit(proj: torch.Tensor, conv_w: torch.Tensor, state: torch.Tensor, row
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and conv_w.dtype == torch.float32 and conv_w.is_contiguous()
     assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (rows, channels)
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (max(taps - 1, 1), channels)
-    _check(_fn("recurrence", "cml_conv_unit")(_p(proj), proj.stride(0), _p(conv_w), _p(state), _p(row_seq), _p(row_pos),
+    _check(_fn("recurrence", "cml_conv_unit")(_p(proj), proj.stride(0), _p(conv_w), _p(state), 1 if update_state else 0, _p(row_seq), _p(row_pos),
                                               _p(seq_row0), _p(seq_slot), _p(out), rows, qk_heads, heads, key_dim, value_dim,
                                               taps, float(q_scale), _stream()), "conv_unit")
 

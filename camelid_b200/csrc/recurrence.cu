@@ -29,9 +29,11 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x));
 // value_dim) before the convolution; `conv_w` [channels, taps] float, the last tap the current
 // token's; `state` [slots, taps - 1, channels] the inputs of the tokens before the step.
 // A warp owns one (row, head of q | k | v). q and k become x / sqrt(sum x^2 + 1e-6), q times
-// q_scale. out [rows, channels] float.
+// q_scale. out [rows, channels] float. With `update_state` (steps in which every sequence brings
+// one row) the warp also moves its channels of the state on by that row; otherwise a later
+// launch replaces the state.
 __global__ void conv_unit_kernel(const float* __restrict__ proj, long ld, const float* __restrict__ conv_w,
-                                 const float* __restrict__ state, const int* __restrict__ row_seq,
+                                 float* __restrict__ state, int update_state, const int* __restrict__ row_seq,
                                  const int* __restrict__ row_pos, const int* __restrict__ seq_row0,
                                  const int* __restrict__ seq_slot, float* __restrict__ out, int rows, int qk_heads,
                                  int heads, int key_dim, int value_dim, int taps, float q_scale) {
@@ -46,7 +48,7 @@ __global__ void conv_unit_kernel(const float* __restrict__ proj, long ld, const 
     if (u < 2 * qk_heads) { c0 = u * key_dim; n = key_dim; }
     else { c0 = 2 * qk_heads * key_dim + (u - 2 * qk_heads) * value_dim; n = value_dim; }
     const int s = row_seq[r], pos = row_pos[r], inside = r - seq_row0[s];
-    const float* st = state + (size_t)seq_slot[s] * (taps - 1) * channels;
+    float* st = state + (size_t)seq_slot[s] * (taps - 1) * channels;
     float ss = 0.f;
     for (int c = c0 + lane; c < c0 + n; c += 32) {
         float acc = 0.f;
@@ -57,6 +59,10 @@ __global__ void conv_unit_kernel(const float* __restrict__ proj, long ld, const 
             if (back <= inside) x = proj[(size_t)(r - back) * ld + c];
             else x = st[(size_t)(taps - 1 + inside - back) * channels + c];
             acc = fmaf(conv_w[(size_t)c * taps + j], x, acc);
+        }
+        if (update_state) {                                // one row per sequence: drop the oldest input, keep this one
+            for (int j = 0; j + 2 < taps; ++j) st[(size_t)j * channels + c] = pos + j + 2 >= taps ? st[(size_t)(j + 1) * channels + c] : 0.f;
+            if (taps > 1) st[(size_t)(taps - 2) * channels + c] = proj[(size_t)r * ld + c];
         }
         acc = silu_f(acc);
         out[(size_t)r * channels + c] = acc;
@@ -70,14 +76,14 @@ __global__ void conv_unit_kernel(const float* __restrict__ proj, long ld, const 
     }
 }
 
-extern "C" int cml_conv_unit(const float* proj, long ld, const float* conv_w, const float* state, const int* row_seq,
+extern "C" int cml_conv_unit(const float* proj, long ld, const float* conv_w, float* state, int update_state, const int* row_seq,
                              const int* row_pos, const int* seq_row0, const int* seq_slot, float* out, int rows, int qk_heads,
                              int heads, int key_dim, int value_dim, int taps, float q_scale, void* stream) {
     if (rows <= 0) return 0;
     if (taps < 1) return CML_ERR_BAD_SIZE;
     const long warps = (long)rows * (2 * qk_heads + heads);
     launch_pdl(conv_unit_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, (cudaStream_t)stream, proj, ld, conv_w, state,
-               row_seq, row_pos, seq_row0, seq_slot, out, rows, qk_heads, heads, key_dim, value_dim, taps, q_scale);
+               update_state, row_seq, row_pos, seq_row0, seq_slot, out, rows, qk_heads, heads, key_dim, value_dim, taps, q_scale);
     return cml_launch_status();
 }
 

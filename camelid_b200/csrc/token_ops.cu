@@ -165,6 +165,79 @@ extern "C" int cml_token_shift(const void* h, int dtype, const void* mix, int mi
 }
 
 // ------------------------------------------------------------------------------------
+// One-token steps: RMS norm and token shift in one launch. Row r is the one new row of sequence
+// row_seq[r], so one block reads the sequence's kept row and replaces it. x[r] += the pending
+// split sums (in split order, written back); n = x[r] / sqrt(mean + eps) * w rounded to the
+// compute type; out[r] = n + (kept - n) * mix (kept: zeros at position 0); kept <- n.
+// The arithmetic is that of the three separate kernels.
+template <typename TW, typename T>
+__global__ void rmsnorm_shift_kernel(float* __restrict__ x, const TW* __restrict__ w, const float* __restrict__ mix,
+                                     float* __restrict__ state, const int* __restrict__ row_seq,
+                                     const int* __restrict__ row_pos, const int* __restrict__ seq_slot, T* __restrict__ out,
+                                     int hidden, float eps, const float* __restrict__ partial, int n_splits,
+                                     size_t split_stride) {
+    __shared__ float red[33];
+    extern __shared__ float rowbuf[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    float* xr = x + (size_t)r * hidden;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float v = xr[c];
+        if (partial) {
+            const float* pp = partial + (size_t)r * hidden + c;
+            for (int s0 = 0; s0 < n_splits; s0 += 8) {
+                float t[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float tv = pp[(size_t)min(s0 + i, n_splits - 1) * split_stride];
+                    t[i] = s0 + i < n_splits ? tv : 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v += t[i];
+            }
+            xr[c] = v;
+        }
+        rowbuf[c] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+    const bool first = row_pos[r] == 0;
+    float* st = state + (size_t)seq_slot[row_seq[r]] * hidden;
+    T* o = out + (size_t)r * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float n = to_f32(from_f32<T>(rowbuf[c] * scale * to_f32(w[c])));
+        const float kept = first ? 0.f : st[c];
+        o[c] = from_f32<T>(n + (kept - n) * mix[c]);
+        st[c] = n;
+    }
+}
+
+extern "C" int cml_rmsnorm_shift(float* x, const void* w, int w_dtype, const float* mix, float* state, const int* row_seq,
+                                 const int* row_pos, const int* seq_slot, void* out, int out_dtype, int rows, int hidden,
+                                 float eps, const float* partial, int n_splits, long split_stride, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int block = hidden >= 2048 ? 1024 : (hidden >= 512 ? 256 : 128);
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 48 * 1024) return CML_ERR_BAD_SIZE;
+#define RS_CASE(TW_, T_, DW_, D_)                                                                                           \
+    if (w_dtype == DW_ && out_dtype == D_) {                                                                                \
+        launch_pdl(rmsnorm_shift_kernel<TW_, T_>, dim3(rows), dim3(block), smem, s, x, (const TW_*)w, mix, state, row_seq, row_pos, \
+                   seq_slot, (T_*)out, hidden, eps, partial, n_splits, (size_t)split_stride);                              \
+        return cml_launch_status();                                                                                         \
+    }
+    RS_CASE(float, float, CML_DTYPE_F32, CML_DTYPE_F32)
+    RS_CASE(float, bf16, CML_DTYPE_F32, CML_DTYPE_BF16)
+    RS_CASE(bf16, float, CML_DTYPE_BF16, CML_DTYPE_F32)
+    RS_CASE(bf16, bf16, CML_DTYPE_BF16, CML_DTYPE_BF16)
+#undef RS_CASE
+    return CML_ERR_BAD_DTYPE;
+}
+
+// ------------------------------------------------------------------------------------
 // h[r] += (base ? base[r] : 0) + vec: the input of one pass over a looped stretch.
 template <typename TW>
 __global__ void add_rows_vec_kernel(float* __restrict__ h, const float* __restrict__ base, const TW* __restrict__ vec,

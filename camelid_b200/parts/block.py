@@ -60,9 +60,11 @@ class PreNormBlock(Part):
             shift = self.shift if part is self.mixer else None
             if not norm.handles_pending:
                 ctx.settle(h)
-            x = norm.forward(ctx, h, allow_row_scale=part.accepts_row_scale and shift is None)
-            if shift is not None:
-                x = shift.forward(ctx, x)
+            x = shift.norm_and_shift(ctx, h, norm) if shift is not None and hasattr(shift, "norm_and_shift") else None
+            if x is None:
+                x = norm.forward(ctx, h, allow_row_scale=part.accepts_row_scale and shift is None)
+                if shift is not None:
+                    x = shift.forward(ctx, x)
             if not part.handles_pending:
                 ctx.settle(h)
             part.forward(ctx, x, h)

@@ -51,6 +51,19 @@ class ParallelMixers(Part):
             b.load(tensors, device, dtype)
         self.out_w = [tensors[f"{self.prefix}{name}.out"].to(device=device, dtype=torch.float32).contiguous()
                       for name in self.names]
+        # Branches that read the same rows through one stacked input matrix each (``w_in``): all of them stacked
+        # once more, so that one product serves every branch; each keeps its rows of it as a view.
+        self.w_in = None
+        self.in_cols = []
+        if len(self.branches) > 1 and all(getattr(b, "w_in", None) is not None for b in self.branches):
+            stacked = torch.cat([b.w_in for b in self.branches], dim=0).contiguous()
+            at = 0
+            for b in self.branches:
+                n = b.w_in.shape[0]
+                b.w_in = stacked[at:at + n]
+                self.in_cols.append((at, n))
+                at += n
+            self.w_in = stacked
 
     def cache_spec(self):
         return [b.cache_spec() for b in self.branches]
@@ -59,5 +72,11 @@ class ParallelMixers(Part):
         return [r for b in self.branches for r in b.query_tile_sizes()]
 
     def forward(self, ctx, x, residual):
-        ys = [b.branch_output(ctx, x, f"branch{i}_out") for i, b in enumerate(self.branches)]
+        if self.w_in is not None:
+            from . import linear
+            proj = linear.product_rows_f32(ctx, x, self.w_in, "branches_proj")
+            ys = [b.branch_output(ctx, x, f"branch{i}_out", proj[:, at:at + n])
+                  for i, (b, (at, n)) in enumerate(zip(self.branches, self.in_cols))]
+        else:
+            ys = [b.branch_output(ctx, x, f"branch{i}_out") for i, b in enumerate(self.branches)]
         ops.norm_combine(list(zip(ys, self.out_w)), residual, self.eps, 1.0 / len(self.branches))

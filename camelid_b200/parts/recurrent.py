@@ -85,9 +85,10 @@ class MatrixMemory(Part):
         return [StateSpec((self.num_heads, self.value_dim + 1, self.key_dim), "float32", "memory"),
                 StateSpec((self.num_heads, self.value_dim + 1), "float32", "maximum")]
 
-    def read_out(self, ctx, x):
+    def read_out(self, ctx, x, proj=None):
         n = ctx.n_rows
-        proj = linear.product_rows_f32(ctx, x, self.w_in, "mm_proj")
+        if proj is None:
+            proj = linear.product_rows_f32(ctx, x, self.w_in, "mm_proj")
         raw = ctx.buffer("mm_raw", (n, self.num_heads, self.value_dim + 2), torch.float32)
         ops.memory_scan(proj, self.cols, self.i_bias, self.f_bias, self.gate_cap, self.key_dim ** -0.5, ctx.state("memory"),
                         ctx.state("maximum"), ctx.seq_row0, ctx.seq_new, ctx.seq_start, ctx.seq_slot, raw, ctx.n_seqs, self.num_heads,
@@ -99,8 +100,8 @@ class MatrixMemory(Part):
     def forward(self, ctx, x, residual):
         linear.add_into_residual(ctx, self.read_out(ctx, x), self.w_o, residual, "o_partial")
 
-    def branch_output(self, ctx, x, name: str):
-        return linear.product_f32(ctx, self.read_out(ctx, x), self.w_o, name)
+    def branch_output(self, ctx, x, name: str, proj=None):
+        return linear.product_f32(ctx, self.read_out(ctx, x, proj), self.w_o, name)
 
 
 @register_part("mixer", "channel_delta")
@@ -178,8 +179,9 @@ class ChannelDelta(Part):
         conv_state = ctx.state("conv")
         qkv = ctx.buffer("cd_qkv", (n, self.channels), torch.float32)
         ops.conv_unit(proj, self.conv_w, conv_state, ctx.row_seq, ctx.row_pos, ctx.seq_row0, ctx.seq_slot, qkv,
-                      self.num_qk_heads, self.num_heads, self.key_dim, self.value_dim, self.key_dim ** -0.5)
-        if self.taps > 1:
+                      self.num_qk_heads, self.num_heads, self.key_dim, self.value_dim, self.key_dim ** -0.5,
+                      update_state=ctx.decode)
+        if self.taps > 1 and not ctx.decode:
             ops.keep_last_rows(proj, 0, self.channels, conv_state, ctx.seq_row0, ctx.seq_new, ctx.seq_start, ctx.seq_slot,
                                ctx.n_seqs)
         raw = ctx.buffer("cd_raw", (n, self.v_width), torch.float32)
@@ -193,5 +195,5 @@ class ChannelDelta(Part):
     def forward(self, ctx, x, residual):
         linear.add_into_residual(ctx, self.read_out(ctx, x), self.w_o, residual, "o_partial")
 
-    def branch_output(self, ctx, x, name: str):
+    def branch_output(self, ctx, x, name: str, proj=None):
         return linear.product_f32(ctx, self.read_out(ctx, x), self.w_o, name)

@@ -30,6 +30,18 @@ class TokenShift(Part):
     def cache_spec(self):
         return StateSpec((1, self.hidden_size), "float32", "shift")
 
+    def norm_and_shift(self, ctx, h, norm):
+        """One-token steps after an RMS norm of the library: norm, shift and the kept row in one launch (the
+        same arithmetic as the parts one after the other). None where that does not apply."""
+        if not (ctx.decode and getattr(norm, "kind", "") == "rmsnorm" and ctx.deferred is None
+                and self.hidden_size * 4 <= 48 * 1024):
+            return None
+        pending, ctx.pending = ctx.pending, None
+        out = ctx.buffer("shifted", (ctx.n_rows, self.hidden_size))
+        ops.rmsnorm_shift(h, norm.weight, norm.eps, self.mix, ctx.state("shift"), ctx.row_seq, ctx.row_pos, ctx.seq_slot, out,
+                          pending)
+        return out
+
     def forward(self, ctx, x):
         state = ctx.state("shift")                                # [slots, 1, hidden]
         out = ctx.buffer("shifted", tuple(x.shape), x.dtype)

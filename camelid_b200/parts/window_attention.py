@@ -89,12 +89,14 @@ class WindowAttention(Part):
             return [ops.attn_tc_tiling(self.num_heads, self.num_kv_heads)[0]]
         return []
 
-    def attend(self, ctx, x):
-        """The gated heads [rows, heads * value_dim] in the compute type: the input of the output projection."""
+    def attend(self, ctx, x, proj=None):
+        """The gated heads [rows, heads * value_dim] in the compute type: the input of the output projection.
+        ``proj``: x @ w_in^T in float32 where a caller has made it already (as columns of a wider product)."""
         n = ctx.n_rows
         group, k_pages, v_pages = ctx.kv()
         table = ctx.block_table(group)
-        proj = linear.product_rows_f32(ctx, x, self.w_in, "wa_proj")
+        if proj is None:
+            proj = linear.product_rows_f32(ctx, x, self.w_in, "wa_proj")
         q = ctx.buffer("wa_q", (n, self.q_width))
         ops.qk_norm_kv_write(proj, self.q_w, self.k_w, self.eps, ctx.row_seq, ctx.row_pos, table, q, k_pages, v_pages,
                              self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim)
@@ -118,6 +120,6 @@ class WindowAttention(Part):
     def forward(self, ctx, x, residual):
         linear.add_into_residual(ctx, self.attend(ctx, x), self.w_o, residual, "o_partial")
 
-    def branch_output(self, ctx, x, name: str):
+    def branch_output(self, ctx, x, name: str, proj=None):
         """The mixer's output as float32 [rows, hidden] or split sums [splits, rows, hidden], in a buffer of its own."""
-        return linear.product_f32(ctx, self.attend(ctx, x), self.w_o, name)
+        return linear.product_f32(ctx, self.attend(ctx, x, proj), self.w_o, name)
