@@ -119,7 +119,7 @@ template <> struct Piece<bf16> {
 };
 
 template <typename T>
-__global__ void window_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+__global__ void __launch_bounds__(1024) window_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                                         const int* __restrict__ table, int max_blocks, const int* __restrict__ row_seq,
                                         const int* __restrict__ row_pos, const float* __restrict__ r1,
                                         const float* __restrict__ r2, const float* __restrict__ gate, long ldg, int gate_col,
@@ -177,16 +177,17 @@ __global__ void window_attention_kernel(const T* __restrict__ q, const T* __rest
 #pragma unroll
         for (int e = 0; e < AW_MAX_VREGS; ++e) acc[e] *= fix;
         const int nk = min(32, j_end - j0);
-#pragma unroll 4
+        // every load unconditional (of a valid row; a key without a page counts with weight zero), so that
+        // the loads of several keys are in flight together
+#pragma unroll 8
         for (int t = 0; t < nk; ++t) {
-            const float pt = __shfl_sync(0xffffffffu, p, t);
             const int pg = __shfl_sync(0xffffffffu, page, t);
-            if (pg < 0) continue;
-            const T* vr = v_pages + (((size_t)pg * kv_heads + g) * CML_PAGE + (j0 + t) % CML_PAGE) * Dv;
+            const float pt = pg < 0 ? 0.f : __shfl_sync(0xffffffffu, p, t);
+            const T* vr = v_pages + (((size_t)max(pg, 0) * kv_heads + g) * CML_PAGE + (j0 + t) % CML_PAGE) * Dv;
 #pragma unroll
             for (int e = 0; e < AW_MAX_VREGS; ++e) {
                 const int c = lane + 32 * e;
-                if (c < Dv) acc[e] = fmaf(pt, to_f32(vr[c]), acc[e]);
+                if (e * 32 < Dv) acc[e] = fmaf(pt, to_f32(vr[c < Dv ? c : 0]), c < Dv ? acc[e] : 0.f);
             }
         }
     }
@@ -225,8 +226,9 @@ extern "C" int cml_window_attention(const void* q, const void* k_pages, const vo
                                     int D, int Dv, int window, float scale, void* stream) {
     if (rows <= 0) return 0;
     if (Dv > 32 * AW_MAX_VREGS || D < 1 || heads % kv_heads) return CML_ERR_BAD_SIZE;
-    // warps per (row, head): one per 64 keys of the window, at most 8; fixed by the window alone
-    const int nw = window > 0 ? (window + 63) / 64 < 8 ? (window + 63) / 64 : 8 : 8;
+    // warps per (row, head): one per round of 32 keys of the window, at most 32 (8 without a window); fixed by
+    // the window alone, so a row's sums do not depend on the step it came in
+    const int nw = window > 0 ? ((window + 31) / 32 < 32 ? (window + 31) / 32 : 32) : 8;
     dim3 grid((unsigned)((long)rows * heads));
     const size_t smem = (size_t)(((D + 3) & ~3) + nw * (Dv + 2)) * sizeof(float);
     if (smem > 48 * 1024 || (long)rows * heads > 0x7fffffffL) return CML_ERR_BAD_SIZE;

@@ -429,7 +429,9 @@ extern "C" int cml_norm_combine(const float* const* y, const void* const* w, con
         br.split_stride[b] = b < n_branches ? split_stride[b] : 0;
     }
     cudaStream_t s = (cudaStream_t)stream;
-    const int block = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    // few rows (one-token steps): many threads per row shorten each thread's chain of columns
+    int block = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    if (rows <= 256 && hidden >= 1024) block = 1024;
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
     if (w_dtype == CML_DTYPE_F32) {
