@@ -95,20 +95,22 @@ extern "C" int cml_qk_norm_kv_write(const float* proj, long ld, const void* q_w,
 // row read in 16-byte pieces where its size allows) and then columns of the values; each warp
 // keeps an online softmax of its run, and the runs are merged in warp order at the end.
 // Dynamic shared memory: the query (D floats), then per warp its maximum, its sum and Dv sums.
-#define AW_MAX_VREGS 8        // value columns per lane: Dv <= 256
+#define AW_MAX_VREGS 8        // value columns per lane at most: Dv <= 256
 
 template <typename T> struct Piece;                 // 16 bytes of a key row as floats
 template <> struct Piece<float> {
     static constexpr int N = 4;
-    static __device__ __forceinline__ void load(const float* p, float* f) {
-        const float4 v = *reinterpret_cast<const float4*>(p);
-        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    static __device__ __forceinline__ uint4 raw(const float* p) { return *reinterpret_cast<const uint4*>(p); }
+    static __device__ __forceinline__ void unpack(const uint4& v, float* f) {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
     }
+    static __device__ __forceinline__ void load(const float* p, float* f) { unpack(raw(p), f); }
 };
 template <> struct Piece<bf16> {
     static constexpr int N = 8;
-    static __device__ __forceinline__ void load(const bf16* p, float* f) {
-        const uint4 v = *reinterpret_cast<const uint4*>(p);
+    static __device__ __forceinline__ uint4 raw(const bf16* p) { return *reinterpret_cast<const uint4*>(p); }
+    static __device__ __forceinline__ void load(const bf16* p, float* f) { unpack(raw(p), f); }
+    static __device__ __forceinline__ void unpack(const uint4& v, float* f) {
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -118,8 +120,8 @@ template <> struct Piece<bf16> {
     }
 };
 
-template <typename T>
-__global__ void __launch_bounds__(1024) window_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+template <typename T, int NV>              // NV: value columns per lane, Dv <= 32 * NV
+__global__ void __launch_bounds__(512) window_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                                         const int* __restrict__ table, int max_blocks, const int* __restrict__ row_seq,
                                         const int* __restrict__ row_pos, const float* __restrict__ r1,
                                         const float* __restrict__ r2, const float* __restrict__ gate, long ldg, int gate_col,
@@ -131,36 +133,54 @@ __global__ void __launch_bounds__(1024) window_attention_kernel(const T* __restr
     const int r = blockIdx.x / heads, hd = blockIdx.x % heads, g = hd / (heads / kv_heads);
     float* qs = aw_sh;
     float* part = aw_sh + ((D + 3) & ~3) + warp * (Dv + 2);
-    for (int c = threadIdx.x; c < D; c += blockDim.x) qs[c] = to_f32(q[((size_t)r * heads + hd) * D + c]);
-    __syncthreads();
+    // what the first round needs besides the query is asked for before the query is staged
     const int i = row_pos[r];
     const int lo = window > 0 ? max(0, i - window + 1) : 0;
     const int rounds = (i - lo) / 32 + 1;
     const int per_warp = (rounds + nw - 1) / nw;
     const int j_first = lo + 32 * warp * per_warp, j_end = min(i + 1, j_first + 32 * per_warp);
     const int* tb = table + (size_t)row_seq[r] * max_blocks;
+    int page_first = -1;
+    if (j_first + lane < j_end) page_first = tb[(j_first + lane) / CML_PAGE];
+    for (int c = threadIdx.x; c < D; c += blockDim.x) qs[c] = to_f32(q[((size_t)r * heads + hd) * D + c]);
+    __syncthreads();
     const float p1 = r1 ? r1[hd] : 0.f, p2 = r2 ? r2[hd] : 0.f;
     const bool pieces = (D % Piece<T>::N) == 0;              // a key row is a whole number of 16-byte pieces
     float m = -INFINITY, l = 0.f;
-    float acc[AW_MAX_VREGS];
+    float acc[NV];
 #pragma unroll
-    for (int e = 0; e < AW_MAX_VREGS; ++e) acc[e] = 0.f;
+    for (int e = 0; e < NV; ++e) acc[e] = 0.f;
+    constexpr int PN = Piece<T>::N;
+    constexpr int KB = NV >= 8 ? 4 : 8;                      // keys whose values are in flight together
     for (int j0 = j_first; j0 < j_end; j0 += 32) {
         const int j = j0 + lane;
         float sc = -INFINITY;
         int page = -1;
         if (j < j_end) {
-            page = tb[j / CML_PAGE];
+            page = j0 == j_first ? page_first : tb[j / CML_PAGE];
             if (page >= 0) {
                 const T* kr = k_pages + (((size_t)page * kv_heads + g) * CML_PAGE + j % CML_PAGE) * D;
                 float dot = 0.f;
                 if (pieces) {
-#pragma unroll 8
-                    for (int c = 0; c < D; c += Piece<T>::N) {
-                        float kf[Piece<T>::N];
+                    // four 16-byte pieces of the key row in flight, then their products
+                    int c = 0;
+                    for (; c + 4 * PN <= D; c += 4 * PN) {
+                        uint4 raw[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) raw[u] = Piece<T>::raw(kr + c + u * PN);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            float kf[PN];
+                            Piece<T>::unpack(raw[u], kf);
+#pragma unroll
+                            for (int x = 0; x < PN; ++x) dot = fmaf(qs[c + u * PN + x], kf[x], dot);
+                        }
+                    }
+                    for (; c < D; c += PN) {
+                        float kf[PN];
                         Piece<T>::load(kr + c, kf);
 #pragma unroll
-                        for (int x = 0; x < Piece<T>::N; ++x) dot = fmaf(qs[c + x], kf[x], dot);
+                        for (int x = 0; x < PN; ++x) dot = fmaf(qs[c + x], kf[x], dot);
                     }
                 } else {
                     for (int c = 0; c < D; ++c) dot = fmaf(qs[c], to_f32(kr[c]), dot);
@@ -175,25 +195,38 @@ __global__ void __launch_bounds__(1024) window_attention_kernel(const T* __restr
         l = l * fix + warp_sum(p);
         m = m_new;
 #pragma unroll
-        for (int e = 0; e < AW_MAX_VREGS; ++e) acc[e] *= fix;
+        for (int e = 0; e < NV; ++e) acc[e] *= fix;
         const int nk = min(32, j_end - j0);
-        // every load unconditional (of a valid row; a key without a page counts with weight zero), so that
-        // the loads of several keys are in flight together
-#pragma unroll 8
-        for (int t = 0; t < nk; ++t) {
-            const int pg = __shfl_sync(0xffffffffu, page, t);
-            const float pt = pg < 0 ? 0.f : __shfl_sync(0xffffffffu, p, t);
-            const T* vr = v_pages + (((size_t)max(pg, 0) * kv_heads + g) * CML_PAGE + (j0 + t) % CML_PAGE) * Dv;
+        // KB keys at a time: their weights and pages by shuffles first, then all their value loads (each
+        // unconditional, of a valid row: a key that does not count has weight zero), then the sums in key order
+        for (int t0 = 0; t0 < nk; t0 += KB) {
+            float pt[KB];
+            const T* vr[KB];
 #pragma unroll
-            for (int e = 0; e < AW_MAX_VREGS; ++e) {
-                const int c = lane + 32 * e;
-                if (e * 32 < Dv) acc[e] = fmaf(pt, to_f32(vr[c < Dv ? c : 0]), c < Dv ? acc[e] : 0.f);
+            for (int u = 0; u < KB; ++u) {
+                const int t = min(t0 + u, nk - 1);
+                const int pg = __shfl_sync(0xffffffffu, page, t);
+                const float pp = __shfl_sync(0xffffffffu, p, t);
+                pt[u] = (t0 + u < nk && pg >= 0) ? pp : 0.f;
+                vr[u] = v_pages + (((size_t)max(pg, 0) * kv_heads + g) * CML_PAGE + (j0 + t) % CML_PAGE) * Dv;
             }
+            float vv[KB][NV];
+#pragma unroll
+            for (int u = 0; u < KB; ++u)
+#pragma unroll
+                for (int e = 0; e < NV; ++e) {
+                    const int c = lane + 32 * e;
+                    vv[u][e] = to_f32(vr[u][c < Dv ? c : 0]);
+                }
+#pragma unroll
+            for (int u = 0; u < KB; ++u)
+#pragma unroll
+                for (int e = 0; e < NV; ++e) acc[e] = fmaf(pt[u], vv[u][e], acc[e]);
         }
     }
     if (lane == 0) { part[0] = m; part[1] = l; }
 #pragma unroll
-    for (int e = 0; e < AW_MAX_VREGS; ++e) {
+    for (int e = 0; e < NV; ++e) {
         const int c = lane + 32 * e;
         if (c < Dv) part[2 + c] = acc[e];
     }
@@ -226,22 +259,22 @@ extern "C" int cml_window_attention(const void* q, const void* k_pages, const vo
                                     int D, int Dv, int window, float scale, void* stream) {
     if (rows <= 0) return 0;
     if (Dv > 32 * AW_MAX_VREGS || D < 1 || heads % kv_heads) return CML_ERR_BAD_SIZE;
-    // warps per (row, head): one per round of 32 keys of the window, at most 32 (8 without a window); fixed by
+    // warps per (row, head): one per round of 32 keys of the window, at most 16 (8 without a window); fixed by
     // the window alone, so a row's sums do not depend on the step it came in
-    const int nw = window > 0 ? ((window + 31) / 32 < 32 ? (window + 31) / 32 : 32) : 8;
+    const int nw = window > 0 ? ((window + 31) / 32 < 16 ? (window + 31) / 32 : 16) : 8;
     dim3 grid((unsigned)((long)rows * heads));
     const size_t smem = (size_t)(((D + 3) & ~3) + nw * (Dv + 2)) * sizeof(float);
     if (smem > 48 * 1024 || (long)rows * heads > 0x7fffffffL) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == CML_DTYPE_F32)
-        launch_pdl(window_attention_kernel<float>, grid, dim3(32 * nw), smem, s, (const float*)q, (const float*)k_pages,
-                   (const float*)v_pages, table, max_blocks, row_seq, row_pos, r1, r2, gate, ldg, gate_col, (float*)out,
-                   heads, kv_heads, D, Dv, window, scale);
-    else if (dtype == CML_DTYPE_BF16)
-        launch_pdl(window_attention_kernel<bf16>, grid, dim3(32 * nw), smem, s, (const bf16*)q, (const bf16*)k_pages,
-                   (const bf16*)v_pages, table, max_blocks, row_seq, row_pos, r1, r2, gate, ldg, gate_col, (bf16*)out,
-                   heads, kv_heads, D, Dv, window, scale);
-    else
-        return CML_ERR_BAD_DTYPE;
+#define AW_CASE(T_, NV_)                                                                                                    \
+    launch_pdl(window_attention_kernel<T_, NV_>, grid, dim3(32 * nw), smem, s, (const T_*)q, (const T_*)k_pages, (const T_*)v_pages, \
+               table, max_blocks, row_seq, row_pos, r1, r2, gate, ldg, gate_col, (T_*)out, heads, kv_heads, D, Dv, window, scale)
+#define AW_SIZES(T_)                                                                                                        \
+    if (Dv <= 32) AW_CASE(T_, 1); else if (Dv <= 64) AW_CASE(T_, 2); else if (Dv <= 128) AW_CASE(T_, 4); else AW_CASE(T_, 8)
+    if (dtype == CML_DTYPE_F32) { AW_SIZES(float); }
+    else if (dtype == CML_DTYPE_BF16) { AW_SIZES(bf16); }
+    else return CML_ERR_BAD_DTYPE;
+#undef AW_SIZES
+#undef AW_CASE
     return cml_launch_status();
 }
