@@ -121,7 +121,7 @@ template <> struct Piece<bf16> {
 };
 
 template <typename T, int NV>              // NV: value columns per lane, Dv <= 32 * NV
-__global__ void __launch_bounds__(512) window_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+__global__ void __launch_bounds__(512, 1) window_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                                         const int* __restrict__ table, int max_blocks, const int* __restrict__ row_seq,
                                         const int* __restrict__ row_pos, const float* __restrict__ r1,
                                         const float* __restrict__ r2, const float* __restrict__ gate, long ldg, int gate_col,
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(512) window_attention_kernel(const T* __restri
 #pragma unroll
     for (int e = 0; e < NV; ++e) acc[e] = 0.f;
     constexpr int PN = Piece<T>::N;
-    constexpr int KB = NV >= 8 ? 4 : 8;                      // keys whose values are in flight together
+    constexpr int KB = NV >= 8 ? 8 : 16;                     // keys whose values are in flight together
     for (int j0 = j_first; j0 < j_end; j0 += 32) {
         const int j = j0 + lane;
         float sc = -INFINITY;
@@ -162,8 +162,21 @@ __global__ void __launch_bounds__(512) window_attention_kernel(const T* __restri
                 const T* kr = k_pages + (((size_t)page * kv_heads + g) * CML_PAGE + j % CML_PAGE) * D;
                 float dot = 0.f;
                 if (pieces) {
-                    // four 16-byte pieces of the key row in flight, then their products
+                    // sixteen 16-byte pieces of the key row in flight (a whole row of 128 bfloat16), then their
+                    // products; what is left in fours and singly. The sum runs over the channels in order either way.
                     int c = 0;
+                    for (; c + 16 * PN <= D; c += 16 * PN) {
+                        uint4 raw[16];
+#pragma unroll
+                        for (int u = 0; u < 16; ++u) raw[u] = Piece<T>::raw(kr + c + u * PN);
+#pragma unroll
+                        for (int u = 0; u < 16; ++u) {
+                            float kf[PN];
+                            Piece<T>::unpack(raw[u], kf);
+#pragma unroll
+                            for (int x = 0; x < PN; ++x) dot = fmaf(qs[c + u * PN + x], kf[x], dot);
+                        }
+                    }
                     for (; c + 4 * PN <= D; c += 4 * PN) {
                         uint4 raw[4];
 #pragma unroll

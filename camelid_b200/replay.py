@@ -43,7 +43,8 @@ def run(args, stdin=None, stdout=None) -> int:
 
     os.makedirs(args.out, exist_ok=True)
     lm = load(args.model, dtype=args.dtype, device="cuda")
-    cache = lm.new_cache(args.max_tokens)
+    # a few pages beyond what was asked: every live request may leave one page partly empty
+    cache = lm.new_cache(args.max_tokens + 16 * 64)
     print(f"[trace_run] model loaded; cache of {cache.book.n_pages} pages ({cache.bytes} bytes)",
           file=sys.stderr, flush=True)
     slots: dict = {}

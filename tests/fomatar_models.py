@@ -58,7 +58,9 @@ WIDE = config(96, 83, [
     delta(72, 160, 2, 1, 4),
     parallel((64, 64, 3, 1, 130, 0.125), (72, 140, 1, 15.0), mlp=128),
 ], loop=None)
-CONFIGS = {"mixed": MIXED, "plain": PLAIN, "from_start": FROM_START, "wide": WIDE}
+# no attention at all (a cache without keys and values), one head, the whole model one looped stretch
+DELTA_ONLY = config(48, 50, [delta(16, 24, 1, 1, 3, mlp=64), delta(8, 8, 3, 3, 2)], loop=(0, 2, 2), bigram=(11, 3, 5))
+CONFIGS = {"mixed": MIXED, "plain": PLAIN, "from_start": FROM_START, "wide": WIDE, "delta_only": DELTA_ONLY}
 
 
 def tensor_shapes(cfg, ranks=(8, 16)):

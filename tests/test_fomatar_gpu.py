@@ -19,8 +19,8 @@ from helpers import assert_same_engine, tokens
 
 pytestmark = pytest.mark.gpu
 
-SEEDS = {"mixed": 11, "plain": 12, "from_start": 13, "wide": 14}
-LENGTHS = {"mixed": 41, "plain": 150, "from_start": 23, "wide": 140}
+SEEDS = {"mixed": 11, "plain": 12, "from_start": 13, "wide": 14, "delta_only": 15}
+LENGTHS = {"mixed": 41, "plain": 150, "from_start": 23, "wide": 140, "delta_only": 70}
 
 
 @pytest.fixture(scope="module")
