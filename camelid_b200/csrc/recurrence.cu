@@ -50,23 +50,52 @@ __global__ void conv_unit_kernel(const float* __restrict__ proj, long ld, const 
     const int s = row_seq[r], pos = row_pos[r], inside = r - seq_row0[s];
     float* st = state + (size_t)seq_slot[s] * (taps - 1) * channels;
     float ss = 0.f;
-    for (int c = c0 + lane; c < c0 + n; c += 32) {
-        float acc = 0.f;
+    // A lane's channels eight at a time, tap by tap: the eight loads of a tap are unconditional (of a valid
+    // place) and in flight together; nothing is stored until every tap has been read.
+    for (int base = c0; base < c0 + n; base += 256) {
+        float acc[8];
+        int cc[8];
+        bool ok[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int c = base + lane + 32 * e;
+            ok[e] = c < c0 + n;
+            cc[e] = ok[e] ? c : c0;
+            acc[e] = 0.f;
+        }
         for (int j = 0; j < taps; ++j) {
             const int back = taps - 1 - j;                 // tokens before this one
             if (back > pos) continue;                      // before the sequence's start
-            float x;
-            if (back <= inside) x = proj[(size_t)(r - back) * ld + c];
-            else x = st[(size_t)(taps - 1 + inside - back) * channels + c];
-            acc = fmaf(conv_w[(size_t)c * taps + j], x, acc);
+            const float* src = back <= inside ? proj + (size_t)(r - back) * ld : st + (size_t)(taps - 1 + inside - back) * channels;
+            float x[8], w[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { x[e] = src[cc[e]]; w[e] = conv_w[(size_t)cc[e] * taps + j]; }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[e], x[e], acc[e]);
         }
-        if (update_state) {                                // one row per sequence: drop the oldest input, keep this one
-            for (int j = 0; j + 2 < taps; ++j) st[(size_t)j * channels + c] = pos + j + 2 >= taps ? st[(size_t)(j + 1) * channels + c] : 0.f;
-            if (taps > 1) st[(size_t)(taps - 2) * channels + c] = proj[(size_t)r * ld + c];
+        if (update_state && taps > 1) {                    // one row per sequence: drop the oldest input, keep this one
+            for (int j = 0; j + 2 < taps; ++j) {
+                float t[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) t[e] = st[(size_t)(j + 1) * channels + cc[e]];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    if (ok[e]) st[(size_t)j * channels + cc[e]] = pos + j + 2 >= taps ? t[e] : 0.f;
+            }
+            float t[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) t[e] = proj[(size_t)r * ld + cc[e]];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (ok[e]) st[(size_t)(taps - 2) * channels + cc[e]] = t[e];
         }
-        acc = silu_f(acc);
-        out[(size_t)r * channels + c] = acc;
-        ss = fmaf(acc, acc, ss);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            if (!ok[e]) continue;
+            const float a = silu_f(acc[e]);
+            out[(size_t)r * channels + cc[e]] = a;
+            ss = fmaf(a, a, ss);
+        }
     }
     if (u < 2 * qk_heads) {
         ss = warp_sum(ss);

@@ -368,7 +368,7 @@ extern "C" int cml_softcap(float* x, long n, float cap, void* stream) {
 // ------------------------------------------------------------------------------------
 // residual[r] += coef * sum over branches b of rmsnorm(y_b[r]) * w_b. Each y_b is a float
 // matrix [splits_b, rows, hidden] whose splits are summed first, in index order. One block
-// per row; the row of each branch is kept in shared memory between the two passes.
+// per row; the rows of all branches are kept in shared memory between the two passes.
 struct CombineBranches {
     const float* y[4];
     const void* w[4];
@@ -378,40 +378,63 @@ struct CombineBranches {
 };
 
 template <typename TW>
-__global__ void norm_combine_kernel(CombineBranches br, float* __restrict__ residual, int hidden, float eps, float coef) {
+__global__ void __launch_bounds__(512) norm_combine_kernel(CombineBranches br, float* __restrict__ residual, int hidden, float eps, float coef) {
     __shared__ float red[33];
-    extern __shared__ float rowbuf[];
+    extern __shared__ float rowbuf[];                  // [branch][hidden]: each branch's row with its splits added
     pdl_wait();
     pdl_launch_dependents();
     const int r = blockIdx.x;
     float* res = residual + (size_t)r * hidden;
-    for (int b = 0; b < br.n; ++b) {
-        const float* y = br.y[b] + (size_t)r * hidden;
-        float ss = 0.f;
-        const int ns = br.splits[b];
-        const size_t stride = br.split_stride[b];
-        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-            // eight splits at a time: the loads are unconditional (of a valid place) and all in flight
-            // before the first add; the adds stay in split order
-            float v = 0.f;
-            for (int s0 = 0; s0 < ns; s0 += 8) {
-                float t[8];
+    float ss[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        // sixteen splits of every branch at a time: the loads are unconditional (of a valid place) and all in
+        // flight before the first add; the adds stay in split order
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        int most = 0;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float tv = y[(size_t)min(s0 + i, ns - 1) * stride + c];
-                    t[i] = s0 + i < ns ? tv : 0.f;
+        for (int b = 0; b < 4; ++b) most = max(most, b < br.n ? br.splits[b] : 0);
+        for (int s0 = 0; s0 < most; s0 += 16) {
+            float t[4][16];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                if (b >= br.n) continue;
+                const float* y = br.y[b] + (size_t)r * hidden + c;
+                const int ns = br.splits[b];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float tv = y[(size_t)min(s0 + i, ns - 1) * br.split_stride[b]];
+                    t[b][i] = s0 + i < ns ? tv : 0.f;
                 }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v += t[i];
             }
-            rowbuf[c] = v;
-            ss = fmaf(v, v, ss);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                if (b >= br.n) continue;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[b] += t[b][i];
+            }
         }
-        ss = block_sum(ss, red);
-        const float scale = coef / sqrtf(ss / (float)hidden + eps);
-        const TW* w = (const TW*)br.w[b];
-        for (int c = threadIdx.x; c < hidden; c += blockDim.x) res[c] += rowbuf[c] * scale * to_f32(w[c]);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            if (b >= br.n) continue;
+            rowbuf[(size_t)b * hidden + c] = v[b];
+            ss[b] = fmaf(v[b], v[b], ss[b]);
+        }
+    }
+    float scale[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        if (b >= br.n) continue;
+        scale[b] = coef / sqrtf(block_sum(ss[b], red) / (float)hidden + eps);
         __syncthreads();
+    }
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float acc = res[c];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            if (b >= br.n) continue;
+            acc += rowbuf[(size_t)b * hidden + c] * scale[b] * to_f32(((const TW*)br.w[b])[c]);
+        }
+        res[c] = acc;
     }
 }
 
@@ -431,8 +454,8 @@ extern "C" int cml_norm_combine(const float* const* y, const void* const* w, con
     cudaStream_t s = (cudaStream_t)stream;
     // few rows (one-token steps): many threads per row shorten each thread's chain of columns
     int block = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-    if (rows <= 256 && hidden >= 1024) block = 1024;
-    const size_t smem = (size_t)hidden * sizeof(float);
+    if (rows <= 256 && hidden >= 1024) block = 512;
+    const size_t smem = (size_t)n_branches * hidden * sizeof(float);
     if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
     if (w_dtype == CML_DTYPE_F32) {
         if (smem > 48 * 1024 && cml_allow_smem<norm_combine_kernel<float>>(smem) != cudaSuccess) return CML_ERR_BAD_SIZE;
