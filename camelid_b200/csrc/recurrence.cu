@@ -200,7 +200,17 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
     const int vc = MODE == 0 ? 2 * p.qk_heads * D + hd * Dv : p.v_col + hd * Dv;
     const float a_rate = MODE == 0 ? expf(p.vec_a[hd]) : 0.f;
     // staging: thread -> (token, key channel) of each array, one value of v, and the scalars
+    // Nothing uses a fetched value before `stage`: a use right behind its load would hold the warp until the
+    // load is back, once per round, instead of behind the tokens in between.
     float rq[PER], rk[PER], rg[MODE == 0 ? PER : 1], rv = 0.f, r1 = 0.f, r2 = 0.f;
+    float bias[MODE == 0 ? PER : 1];                   // dt_bias of the channels this thread stages (the same every round)
+    if (MODE == 0) {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int d = (threadIdx.x + 128 * e) % DPAD;
+            bias[e] = p.vec_b[hd * D + (d < D ? d : 0)];
+        }
+    }
     auto fetch = [&](int t0) {
         const int nt = min(SCAN_TOKENS, n - t0);
 #pragma unroll
@@ -211,14 +221,12 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
             const int dd = ok ? d : 0;
             rq[e] = p.in_a[r * p.lda + qc + dd];
             rk[e] = p.in_a[r * p.lda + kc + dd];
-            if (MODE == 0) rg[e] = p.in_c[r * p.ldc + hd * D + dd] + p.vec_b[hd * D + dd];
-            if (!ok) rq[e] = rk[e] = 0.f;              // channels beyond D stay out of every sum
+            if (MODE == 0) rg[e] = p.in_c[r * p.ldc + hd * D + dd];
         }
         {
             const int t = threadIdx.x / SCAN_COLS, cc = blockIdx.z * SCAN_COLS + threadIdx.x % SCAN_COLS;
             const bool ok = t < nt && cc < Dv;
             rv = p.in_a[(size_t)(row0 + t0 + (ok ? t : 0)) * p.lda + vc + (ok ? cc : 0)];
-            if (!ok) rv = (MODE == 1 && cc == Dv) ? 1.0f : 0.f;          // the column of n has v = 1
         }
         if (threadIdx.x < SCAN_TOKENS) {
             const size_t r = (size_t)(row0 + t0 + (threadIdx.x < nt ? threadIdx.x : 0));
@@ -231,11 +239,15 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
         for (int e = 0; e < PER; ++e) {
             const int idx = threadIdx.x + 128 * e, t = idx / DPAD, d = idx % DPAD;
             const int at = (d / DS) * SL + d % DS;
-            sq[t][at] = MODE == 1 ? rq[e] * p.q_scale : rq[e];
-            sk[t][at] = rk[e];
-            if (MODE == 0) sg[t][at] = expf(-a_rate * softplus_f(rg[e]));
+            const bool in = d < D;                     // channels beyond D stay out of every sum
+            sq[t][at] = in ? (MODE == 1 ? rq[e] * p.q_scale : rq[e]) : 0.f;
+            sk[t][at] = in ? rk[e] : 0.f;
+            if (MODE == 0) sg[t][at] = expf(-a_rate * softplus_f(rg[e] + bias[e]));
         }
-        sv[threadIdx.x / SCAN_COLS][threadIdx.x % SCAN_COLS] = rv;
+        {
+            const int cc = blockIdx.z * SCAN_COLS + threadIdx.x % SCAN_COLS;
+            sv[threadIdx.x / SCAN_COLS][threadIdx.x % SCAN_COLS] = cc < Dv ? rv : ((MODE == 1 && cc == Dv) ? 1.0f : 0.f);   // the column of n has v = 1
+        }
         if (threadIdx.x < SCAN_TOKENS) {
             if (MODE == 0) s1[threadIdx.x] = sigmoid_f(r1);
             else {
@@ -258,24 +270,26 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
             float o = 0.f;
             if (MODE == 0) {
                 const float* gg = &sg[t][slice * SL];
-                float dot = 0.f;
+                float d4[4] = {0.f, 0.f, 0.f, 0.f};       // four chains of multiply-adds, always in this order
 #pragma unroll
                 for (int i = 0; i < DS; i += 4) {
                     const float4 gv = *reinterpret_cast<const float4*>(gg + i), kv = *reinterpret_cast<const float4*>(kq + i);
                     S[i] *= gv.x; S[i + 1] *= gv.y; S[i + 2] *= gv.z; S[i + 3] *= gv.w;
-                    dot = fmaf(S[i], kv.x, dot); dot = fmaf(S[i + 1], kv.y, dot);
-                    dot = fmaf(S[i + 2], kv.z, dot); dot = fmaf(S[i + 3], kv.w, dot);
+                    d4[0] = fmaf(S[i], kv.x, d4[0]); d4[1] = fmaf(S[i + 1], kv.y, d4[1]);
+                    d4[2] = fmaf(S[i + 2], kv.z, d4[2]); d4[3] = fmaf(S[i + 3], kv.w, d4[3]);
                 }
-                dot = slices_sum(dot);
+                const float dot = slices_sum((d4[0] + d4[1]) + (d4[2] + d4[3]));
                 const float u = s1[t] * (vcol - dot);
+                float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int i = 0; i < DS; i += 4) {
                     const float4 kv = *reinterpret_cast<const float4*>(kq + i), qv = *reinterpret_cast<const float4*>(qq + i);
                     S[i] = fmaf(kv.x, u, S[i]); S[i + 1] = fmaf(kv.y, u, S[i + 1]);
                     S[i + 2] = fmaf(kv.z, u, S[i + 2]); S[i + 3] = fmaf(kv.w, u, S[i + 3]);
-                    o = fmaf(S[i], qv.x, o); o = fmaf(S[i + 1], qv.y, o); o = fmaf(S[i + 2], qv.z, o); o = fmaf(S[i + 3], qv.w, o);
+                    o4[0] = fmaf(S[i], qv.x, o4[0]); o4[1] = fmaf(S[i + 1], qv.y, o4[1]);
+                    o4[2] = fmaf(S[i + 2], qv.z, o4[2]); o4[3] = fmaf(S[i + 3], qv.w, o4[3]);
                 }
-                o = slices_sum(o);
+                o = slices_sum((o4[0] + o4[1]) + (o4[2] + o4[3]));
                 if (live && slice == 0) p.out[(size_t)(row0 + t0 + t) * heads * Dv + hd * Dv + c] = o;
             } else {
                 const float fm = s2[t] + m;
@@ -283,14 +297,16 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
                 const float a = expf(fm - m_new);
                 const float bv = expf(s1[t] - m_new) * vcol;
                 m = m_new;
+                float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int i = 0; i < DS; i += 4) {
                     const float4 kv = *reinterpret_cast<const float4*>(kq + i), qv = *reinterpret_cast<const float4*>(qq + i);
                     S[i] = fmaf(a, S[i], bv * kv.x); S[i + 1] = fmaf(a, S[i + 1], bv * kv.y);
                     S[i + 2] = fmaf(a, S[i + 2], bv * kv.z); S[i + 3] = fmaf(a, S[i + 3], bv * kv.w);
-                    o = fmaf(S[i], qv.x, o); o = fmaf(S[i + 1], qv.y, o); o = fmaf(S[i + 2], qv.z, o); o = fmaf(S[i + 3], qv.w, o);
+                    o4[0] = fmaf(S[i], qv.x, o4[0]); o4[1] = fmaf(S[i + 1], qv.y, o4[1]);
+                    o4[2] = fmaf(S[i + 2], qv.z, o4[2]); o4[3] = fmaf(S[i + 3], qv.w, o4[3]);
                 }
-                o = slices_sum(o);
+                o = slices_sum((o4[0] + o4[1]) + (o4[2] + o4[3]));
                 if (live && slice == 0) {
                     float* orow = p.out + ((size_t)(row0 + t0 + t) * heads + hd) * (Dv + 2);
                     orow[c] = o;
