@@ -96,10 +96,11 @@ _SIGNATURES = {
     ("token_ops", "cml_norm_combine"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_float,
                                         c_float, c_void_p],
     ("recurrence", "cml_conv_unit"): [c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                      c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_long, c_void_p, c_void_p,
+                                      c_void_p, c_void_p],
     ("recurrence", "cml_delta_scan"): [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_long, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                       c_int, c_void_p],
+                                       c_int, c_int, c_void_p],
     ("recurrence", "cml_memory_scan"): [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
                                         c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                         c_int, c_int, c_int, c_void_p],
@@ -443,12 +444,14 @@ def norm_combine(branches: list, residual: torch.Tensor, eps: float, coef: float
 
 def conv_unit(proj: torch.Tensor, conv_w: torch.Tensor, state: torch.Tensor, row_seq, row_pos, seq_row0, seq_slot,
               out: torch.Tensor, qk_heads: int, heads: int, key_dim: int, value_dim: int, q_scale: float,
-              update_state: bool = False):
+              update_state: bool = False, decay=None):
     """Short causal convolution + SiLU over the q, k, v channels at the start of ``proj``'s columns
     (float32), then unit norm of q and k per head, q times ``q_scale``. ``conv_w`` float32
     [channels, taps]; ``state`` float32 [slots, taps - 1, channels]: the inputs before the step. With
     ``update_state`` (only where every sequence brings exactly one row) the state moves on by that row here;
-    otherwise ``keep_last_rows`` does that afterwards."""
+    otherwise ``keep_last_rows`` does that afterwards. ``decay`` = (inputs float32 [rows, heads * key_dim] view, a_log,
+    dt_bias, out float32 [rows, heads * key_dim]): the same launch also makes the delta rule's decays
+    exp(-exp(a_log[head]) softplus(x + dt_bias))."""
     _dev(proj, conv_w, state, row_seq, row_pos, seq_row0, seq_slot, out)
     channels, taps = conv_w.shape
     rows = out.shape[0]
@@ -456,16 +459,25 @@ def conv_unit(proj: torch.Tensor, conv_w: torch.Tensor, state: torch.Tensor, row
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and conv_w.dtype == torch.float32 and conv_w.is_contiguous()
     assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (rows, channels)
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (max(taps - 1, 1), channels)
+    d_in = d_alog = d_bias = d_out = None
+    if decay is not None:
+        d_in, d_alog, d_bias, d_out = decay
+        _dev(d_in, d_alog, d_bias, d_out)
+        assert d_in.dtype == torch.float32 and d_in.stride(1) == 1 and d_in.shape == (rows, heads * key_dim)
+        assert d_out.dtype == torch.float32 and d_out.is_contiguous() and d_out.shape == (rows, heads * key_dim)
+        assert d_alog.numel() == heads and d_bias.numel() == heads * key_dim
     _check(_fn("recurrence", "cml_conv_unit")(_p(proj), proj.stride(0), _p(conv_w), _p(state), 1 if update_state else 0, _p(row_seq), _p(row_pos),
                                               _p(seq_row0), _p(seq_slot), _p(out), rows, qk_heads, heads, key_dim, value_dim,
-                                              taps, float(q_scale), _stream()), "conv_unit")
+                                              taps, float(q_scale), _p(d_in), d_in.stride(0) if d_in is not None else 0,
+                                              _p(d_alog), _p(d_bias), _p(d_out), _stream()), "conv_unit")
 
 
 def delta_scan(qkv: torch.Tensor, beta_in: torch.Tensor, beta_col: int, decay_in: torch.Tensor, a_log, dt_bias,
                state: torch.Tensor, seq_row0, seq_new, seq_start, seq_slot, out: torch.Tensor, n_seqs: int, heads: int,
-               qk_heads: int, key_dim: int, value_dim: int):
+               qk_heads: int, key_dim: int, value_dim: int, decay_ready: bool = False):
     """The gated delta rule over each sequence's new rows; ``state`` float32 [slots, heads, value_dim,
-    key_dim] (column by column) is read and replaced; ``out`` float32 [rows, heads * value_dim] = S^T q."""
+    key_dim] (column by column) is read and replaced; ``out`` float32 [rows, heads * value_dim] = S^T q.
+    ``decay_ready``: ``decay_in`` holds the decays themselves (``conv_unit`` made them), not their inputs."""
     _dev(qkv, beta_in, decay_in, a_log, dt_bias, state, seq_row0, seq_new, seq_start, seq_slot, out)
     for t in (qkv, beta_in, decay_in, out, state, a_log, dt_bias):
         assert t.dtype == torch.float32 and t.stride(-1) == 1
@@ -474,7 +486,7 @@ def delta_scan(qkv: torch.Tensor, beta_in: torch.Tensor, beta_col: int, decay_in
     _check(_fn("recurrence", "cml_delta_scan")(_p(qkv), qkv.stride(0), _p(beta_in), beta_in.stride(0), beta_col, _p(decay_in),
                                                decay_in.stride(0), _p(a_log), _p(dt_bias), _p(state), _p(seq_row0),
                                                _p(seq_new), _p(seq_start), _p(seq_slot), _p(out), n_seqs, heads, qk_heads,
-                                               key_dim, value_dim, _stream()), "delta_scan")
+                                               key_dim, value_dim, 1 if decay_ready else 0, _stream()), "delta_scan")
 
 
 def memory_scan(proj: torch.Tensor, cols: tuple, i_bias, f_bias, cap: float, q_scale: float, state: torch.Tensor,

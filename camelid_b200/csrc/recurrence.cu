@@ -36,13 +36,26 @@ __global__ void conv_unit_kernel(const float* __restrict__ proj, long ld, const 
                                  float* __restrict__ state, int update_state, const int* __restrict__ row_seq,
                                  const int* __restrict__ row_pos, const int* __restrict__ seq_row0,
                                  const int* __restrict__ seq_slot, float* __restrict__ out, int rows, int qk_heads,
-                                 int heads, int key_dim, int value_dim, int taps, float q_scale) {
+                                 int heads, int key_dim, int value_dim, int taps, float q_scale,
+                                 const float* __restrict__ decay_in, long ldd, const float* __restrict__ a_log,
+                                 const float* __restrict__ dt_bias, float* __restrict__ decay_out) {
     pdl_wait();
     pdl_launch_dependents();
-    const int units = 2 * qk_heads + heads;
+    const int units = 2 * qk_heads + heads + (decay_in ? heads : 0);
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= rows * units) return;
     const int r = warp / units, u = warp % units;
+    if (u >= 2 * qk_heads + heads) {
+        // the decays of one (row, head), once for all the scan's blocks of that head:
+        // g = exp(-exp(a_log[head]) softplus(x + dt_bias))
+        const int hd = u - 2 * qk_heads - heads;
+        const float rate = expf(a_log[hd]);
+        for (int d = lane; d < key_dim; d += 32) {
+            const float x = decay_in[(size_t)r * ldd + hd * key_dim + d] + dt_bias[hd * key_dim + d];
+            decay_out[((size_t)r * heads + hd) * key_dim + d] = expf(-rate * softplus_f(x));
+        }
+        return;
+    }
     const int channels = 2 * qk_heads * key_dim + heads * value_dim;
     int c0, n;
     if (u < 2 * qk_heads) { c0 = u * key_dim; n = key_dim; }
@@ -105,14 +118,18 @@ __global__ void conv_unit_kernel(const float* __restrict__ proj, long ld, const 
     }
 }
 
+// decay_in (may be null) [rows, ldd] (heads x key_dim): the decays' inputs; decay_out [rows, heads x key_dim] gets
+// g = exp(-exp(a_log[head]) softplus(x + dt_bias)), what the delta-rule scan multiplies its state by.
 extern "C" int cml_conv_unit(const float* proj, long ld, const float* conv_w, float* state, int update_state, const int* row_seq,
                              const int* row_pos, const int* seq_row0, const int* seq_slot, float* out, int rows, int qk_heads,
-                             int heads, int key_dim, int value_dim, int taps, float q_scale, void* stream) {
+                             int heads, int key_dim, int value_dim, int taps, float q_scale, const float* decay_in, long ldd,
+                             const float* a_log, const float* dt_bias, float* decay_out, void* stream) {
     if (rows <= 0) return 0;
     if (taps < 1) return CML_ERR_BAD_SIZE;
-    const long warps = (long)rows * (2 * qk_heads + heads);
+    const long warps = (long)rows * (2 * qk_heads + heads + (decay_in ? heads : 0));
     launch_pdl(conv_unit_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, (cudaStream_t)stream, proj, ld, conv_w, state,
-               update_state, row_seq, row_pos, seq_row0, seq_slot, out, rows, qk_heads, heads, key_dim, value_dim, taps, q_scale);
+               update_state, row_seq, row_pos, seq_row0, seq_slot, out, rows, qk_heads, heads, key_dim, value_dim, taps, q_scale, decay_in, ldd,
+               a_log, dt_bias, decay_out);
     return cml_launch_status();
 }
 
@@ -128,7 +145,7 @@ extern "C" int cml_conv_unit(const float* proj, long ld, const float* conv_w, fl
 //
 // MODE 0, gated delta rule. in_a = qkv [rows, lda]: unit q (qk_heads x D), unit k, v (heads x Dv)
 // from conv_unit_kernel; in_b [rows, ldb]: beta before the sigmoid at column b_col + head;
-// in_c [rows, ldc] (heads x D): decay input, g = exp(-exp(a_log[head]) softplus(x + dt_bias)).
+// in_c [rows, ldc] (heads x D): the decays g (decay_ready), or their input: g = exp(-exp(a_log[head]) softplus(x + dt_bias)).
 // state [slots, heads, Dv, D]. out [rows, heads x Dv] = S^T q.
 // MODE 1, matrix memory. in_a = proj [rows, lda] with q at q_col (heads x D), k at k_col, v at
 // v_col (heads x Dv), gate inputs at i_col + head and f_col + head (before bias and cap).
@@ -150,6 +167,7 @@ struct ScanParams {
     int heads, qk_heads, D, Dv;
     int q_col, k_col, v_col, i_col, f_col;
     float cap, q_scale;
+    int decay_ready;              // in_c holds the decays themselves (conv_unit_kernel made them)
 };
 
 __device__ __forceinline__ float slices_sum(float v) {
@@ -198,13 +216,13 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
     const int qc = MODE == 0 ? g * D : p.q_col + hd * D;
     const int kc = MODE == 0 ? (p.qk_heads + g) * D : p.k_col + hd * D;
     const int vc = MODE == 0 ? 2 * p.qk_heads * D + hd * Dv : p.v_col + hd * Dv;
-    const float a_rate = MODE == 0 ? expf(p.vec_a[hd]) : 0.f;
+    const float a_rate = (MODE == 0 && !p.decay_ready) ? expf(p.vec_a[hd]) : 0.f;
     // staging: thread -> (token, key channel) of each array, one value of v, and the scalars
     // Nothing uses a fetched value before `stage`: a use right behind its load would hold the warp until the
     // load is back, once per round, instead of behind the tokens in between.
     float rq[PER], rk[PER], rg[MODE == 0 ? PER : 1], rv = 0.f, r1 = 0.f, r2 = 0.f;
     float bias[MODE == 0 ? PER : 1];                   // dt_bias of the channels this thread stages (the same every round)
-    if (MODE == 0) {
+    if (MODE == 0 && !p.decay_ready) {
 #pragma unroll
         for (int e = 0; e < PER; ++e) {
             const int d = (threadIdx.x + 128 * e) % DPAD;
@@ -242,7 +260,7 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
             const bool in = d < D;                     // channels beyond D stay out of every sum
             sq[t][at] = in ? (MODE == 1 ? rq[e] * p.q_scale : rq[e]) : 0.f;
             sk[t][at] = in ? rk[e] : 0.f;
-            if (MODE == 0) sg[t][at] = expf(-a_rate * softplus_f(rg[e] + bias[e]));
+            if (MODE == 0) sg[t][at] = p.decay_ready ? rg[e] : expf(-a_rate * softplus_f(rg[e] + bias[e]));
         }
         {
             const int cc = blockIdx.z * SCAN_COLS + threadIdx.x % SCAN_COLS;
@@ -349,13 +367,13 @@ static int launch_scan(const ScanParams& p, int n_seqs, cudaStream_t s) {
 extern "C" int cml_delta_scan(const float* qkv, long ldq, const float* beta_in, long ldb, int beta_col, const float* decay_in,
                               long ldd, const float* a_log, const float* dt_bias, float* state, const int* seq_row0,
                               const int* seq_new, const int* seq_start, const int* seq_slot, float* out, int n_seqs, int heads,
-                              int qk_heads, int D, int Dv, void* stream) {
+                              int qk_heads, int D, int Dv, int decay_ready, void* stream) {
     if (qk_heads < 1 || heads % qk_heads) return CML_ERR_BAD_SIZE;
     ScanParams p = {};
     p.in_a = qkv; p.lda = ldq; p.in_b = beta_in; p.ldb = ldb; p.b_col = beta_col; p.in_c = decay_in; p.ldc = ldd;
     p.vec_a = a_log; p.vec_b = dt_bias; p.state = state; p.state_m = nullptr;
     p.seq_row0 = seq_row0; p.seq_new = seq_new; p.seq_start = seq_start; p.seq_slot = seq_slot; p.out = out;
-    p.heads = heads; p.qk_heads = qk_heads; p.D = D; p.Dv = Dv;
+    p.heads = heads; p.qk_heads = qk_heads; p.D = D; p.Dv = Dv; p.decay_ready = decay_ready;
     return launch_scan<0>(p, n_seqs, (cudaStream_t)stream);
 }
 

@@ -393,7 +393,12 @@ __global__ void __launch_bounds__(512) norm_combine_kernel(CombineBranches br, f
         int most = 0;
 #pragma unroll
         for (int b = 0; b < 4; ++b) most = max(most, b < br.n ? br.splits[b] : 0);
-        for (int s0 = 0; s0 < most; s0 += 16) {
+        if (most == 1) {                               // whole rows (prompts): one load per branch
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+                if (b < br.n) v[b] = br.y[b][(size_t)r * hidden + c];
+        }
+        for (int s0 = 0; most > 1 && s0 < most; s0 += 16) {
             float t[4][16];
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
@@ -455,6 +460,7 @@ extern "C" int cml_norm_combine(const float* const* y, const void* const* w, con
     // few rows (one-token steps): many threads per row shorten each thread's chain of columns
     int block = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     if (rows <= 256 && hidden >= 1024) block = 512;
+    else if (block > 256) block = 256;               // many rows: several blocks per SM
     const size_t smem = (size_t)n_branches * hidden * sizeof(float);
     if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
     if (w_dtype == CML_DTYPE_F32) {

@@ -178,16 +178,17 @@ class ChannelDelta(Part):
         high = linear.product_rows_f32(ctx, low, self.w_high, "cd_high")          # decay inputs, then gate inputs
         conv_state = ctx.state("conv")
         qkv = ctx.buffer("cd_qkv", (n, self.channels), torch.float32)
+        decays = ctx.buffer("cd_decay", (n, self.decay_width), torch.float32)
         ops.conv_unit(proj, self.conv_w, conv_state, ctx.row_seq, ctx.row_pos, ctx.seq_row0, ctx.seq_slot, qkv,
                       self.num_qk_heads, self.num_heads, self.key_dim, self.value_dim, self.key_dim ** -0.5,
-                      update_state=ctx.decode)
+                      update_state=ctx.decode, decay=(high[:, :self.decay_width], self.a_log, self.dt_bias, decays))
         if self.taps > 1 and not ctx.decode:
             ops.keep_last_rows(proj, 0, self.channels, conv_state, ctx.seq_row0, ctx.seq_new, ctx.seq_start, ctx.seq_slot,
                                ctx.n_seqs)
         raw = ctx.buffer("cd_raw", (n, self.v_width), torch.float32)
-        ops.delta_scan(qkv, proj, self.channels, high[:, :self.decay_width], self.a_log, self.dt_bias, ctx.state("memory"),
+        ops.delta_scan(qkv, proj, self.channels, decays, self.a_log, self.dt_bias, ctx.state("memory"),
                        ctx.seq_row0, ctx.seq_new, ctx.seq_start, ctx.seq_slot, raw, ctx.n_seqs, self.num_heads,
-                       self.num_qk_heads, self.key_dim, self.value_dim)
+                       self.num_qk_heads, self.key_dim, self.value_dim, decay_ready=True)
         out = ctx.buffer("cd_out", (n, self.v_width))
         ops.head_norm_gate(raw, False, self.norm_w, False, high, self.decay_width, out, self.num_heads, self.value_dim, self.eps)
         return out

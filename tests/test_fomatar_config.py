@@ -135,3 +135,21 @@ def test_plain_forward_is_causal_and_loops():
     assert layers.shape[0] == 8 and torch.isfinite(full).all()
     assert torch.allclose(pf.forward(toks[:9], P, MIXED), full[:9], atol=1e-9)
     assert float(full.abs().max()) <= MIXED["logit_softcap"]
+
+
+def test_random_weights_folder_of_the_library(tmp_path):
+    """``write_random_model`` draws every tensor of the design by its init rule: gates, rates and fractions in
+    their working ranges, so the plain implementation stays finite on them."""
+    import json
+    from camelid_b200.weights.random_init import write_random_model
+    from camelid_b200.weights.safetensors_io import ModelFiles
+    folder = write_random_model(str(tmp_path / "m"), MIXED, seed=3)
+    files = ModelFiles(folder)
+    P = {n: files.tensor(n).to(torch.float64) for n in files.names()}
+    files.close()
+    assert set(P) == set(tensor_shapes(MIXED, ranks=(8, 8)))
+    assert float(P["l0.mix.left.r2"].min()) > 0 and float(P["l0.shift"].min()) > 0
+    with open(tmp_path / "m" / "config.json") as f:
+        cfg = json.load(f)
+    out = pf.forward([1, 5, 9, 2, 7, 7, 3], P, cfg)
+    assert torch.isfinite(out).all() and float(out.abs().max()) > 1e-3

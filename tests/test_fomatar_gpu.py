@@ -176,6 +176,18 @@ def test_greedy_generation_through_the_entry_point(cuda, folders, dtype):
                 seq.append(tok)
 
 
+def test_weights_drawn_on_the_device_match_the_folder(cuda, tmp_path):
+    """``from_random`` (what the benchmark uses) and a folder written on the host hold the same model."""
+    import camelid_b200
+    from camelid_b200.weights.random_init import write_random_model
+    cfg = CONFIGS["mixed"]
+    folder = write_random_model(str(tmp_path / "m"), cfg, seed=5)
+    a = camelid_b200.load(folder, dtype="bfloat16")
+    b = camelid_b200.from_random(cfg, seed=5, dtype="bfloat16")
+    prompts = [tokens(1, 12, cfg["vocab"]), tokens(2, 3, cfg["vocab"])]
+    assert a.generate(prompts, max_tokens=6) == b.generate(prompts, max_tokens=6)
+
+
 def test_trace_runner_replays_a_fomatar_model(cuda, folders, tmp_path):
     folder, P = folders["from_start"]
     cfg = CONFIGS["from_start"]
