@@ -122,8 +122,6 @@ class FomatarConfig:
                     "times": _positive(loop, "times", "loop")}
             if not 0 <= loop["start"] <= loop["stop"] <= len(layers):
                 raise ConfigError("loop", f"layers {loop['start']}..{loop['stop']} are not a stretch of the {len(layers)} layers")
-            if loop["start"] == loop["stop"]:
-                loop = None
         return cls(copy.deepcopy(d), vocab, width, eps, softcap, bigram, tuple(layers), loop)
 
     def to_dict(self) -> dict:
@@ -169,6 +167,10 @@ def fomatar_plan(cfg: FomatarConfig) -> ModelPlan:
     if cfg.loop is None:
         schedule = [ScheduleEntry(i) for i in range(n)]
         pass_input = None
+    elif cfg.loop["start"] == cfg.loop["stop"]:
+        # an empty stretch: no layer starts a pass, so nothing is added; the passes' tensor is still the model's
+        schedule = [ScheduleEntry(i) for i in range(n)]
+        pass_input = PartSpec("loop_step", {"hidden_size": cfg.width, "passes": cfg.loop["times"], "tensor": "loop.step"})
     else:
         lo, hi, times = cfg.loop["start"], cfg.loop["stop"], cfg.loop["times"]
         schedule = [ScheduleEntry(i) for i in range(lo)]

@@ -106,7 +106,7 @@ def test_portions_of_a_prompt(cuda, folders, name, cut):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mixed", "plain"])
+@pytest.mark.parametrize("name", ["mixed", "plain", "wide"])
 def test_unequal_batch_against_each_alone(cuda, folders, name, dtype):
     """Prompts of 1, 17 and 90 tokens start together, are decoded together and end one after the other."""
     from camelid_b200.engine.model import StepEntry
