@@ -305,6 +305,56 @@ def test_window_attention_kernels_at_the_windows_edge(cuda, cut):
     assert float((got - ref).abs().max()) < 2e-5 * max(1.0, float(ref.abs().max()))
 
 
+@pytest.mark.parametrize("D,group,window", [(64, 3, 70), (128, 2, 200), (128, 1, 33)])
+def test_prompt_attention_on_tensor_cores_against_the_plain_formula(cuda, D, group, window):
+    """bfloat16 prompts with keys and values of 64 or 128 channels take the tcgen05 kernel with the distance penalty in
+    its softmax: against the plain formula on the same bfloat16 q, k, v (two sequences, the second from position 0 too)."""
+    from camelid_b200.csrc import ops
+    from camelid_b200.parts import linear
+    gen = torch.Generator().manual_seed(7)
+    G, lens = 2, [230, 67]
+    H = G * group
+    r1, r2 = torch.rand(H, generator=gen) * 2.5, torch.rand(H, generator=gen) * 0.5
+    scale = D ** -0.5
+    rows, tiles_hpc_chunks = sum(lens), ops.attn_tc_tiling(H, G)
+    tile_rows, hpc, chunks = tiles_hpc_chunks
+    q = (torch.randn(rows, H, D, generator=gen)).to(torch.bfloat16)
+    k = (torch.randn(rows, G, D, generator=gen)).to(torch.bfloat16)
+    v = (torch.randn(rows, G, D, generator=gen)).to(torch.bfloat16)
+    ref, at = [], 0
+    for n in lens:
+        ref.append(pf.window_scores_core(q[at:at + n].double(), k[at:at + n].double(), v[at:at + n].double(), scale, window,
+                                         r1.double(), r2.double()).reshape(n, H * D))
+        at += n
+    ref = torch.cat(ref)
+    pages = [(n + 63) // 64 for n in lens]
+    width = max(pages)
+    table = torch.full((2, width), -1, dtype=torch.int32)
+    table[0, :pages[0]] = torch.arange(pages[0]) + pages[1]
+    table[1, :pages[1]] = torch.arange(pages[1])
+    table = table.to(cuda)
+    kp = torch.zeros(sum(pages), G, 64, D, dtype=torch.bfloat16, device=cuda)
+    vp = torch.zeros_like(kp)
+    a = arrays(cuda, [0, 0], lens)
+    proj = torch.cat([q.reshape(rows, -1), k.reshape(rows, -1), v.reshape(rows, -1)], 1).float().to(cuda)
+    qn = torch.empty(rows, H * D, dtype=torch.bfloat16, device=cuda)
+    ops.qk_norm_kv_write(proj, None, None, 1e-6, a["row_seq"], a["row_pos"], table, qn, kp, vp, H, G, D, D)
+    tile_seq = [s for s, n in enumerate(lens) for _ in range(0, n, tile_rows)]
+    tile_q0 = [q0 for n in lens for q0 in range(0, n, tile_rows)]
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device=cuda)      # noqa: E731
+    out = torch.empty(rows, H * D, dtype=torch.bfloat16, device=cuda)
+    assert ops.attn_tc_usable(qn, out, D)
+    ops.attn_prefill_tc(qn, out, kp, vp, table, dev(tile_seq), dev(tile_q0), len(tile_seq), a["seq_row0"], a["seq_start"],
+                        a["seq_new"], H, G, D, tile_rows, hpc, chunks, window, scale, linear._err_word(cuda), r1.to(cuda), r2.to(cuda))
+    plain_kernel = torch.empty_like(out)
+    ops.window_attention(qn, kp, vp, table, a["row_seq"], a["row_pos"], r1.to(cuda), r2.to(cuda), None, 0, plain_kernel, H, G, D, D,
+                         window, scale)
+    linear.check_errors()
+    for got, what in ((out, "tensor cores"), (plain_kernel, "plain kernel")):
+        err = float((got.cpu().double() - ref).abs().max())
+        assert err < 3e-2, f"{what}: {err}"
+
+
 @pytest.mark.parametrize("cut", [[300], [3, 2, 200], [1]])
 def test_scan_kernels_keep_a_far_key(cuda, cut):
     """A key written at token 2 and asked for at token 290, with decays close to one: the state carries it through
