@@ -251,6 +251,14 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
             if (MODE == 0) r1 = p.in_b[r * p.ldb + p.b_col + hd];
             else { r1 = p.in_a[r * p.lda + p.i_col + hd]; r2 = p.in_a[r * p.lda + p.f_col + hd]; }
         }
+        // The loads stay here, ahead of the tokens that are worked on meanwhile: without this the compiler moves
+        // them down to their first use, where the warp would wait for them. (No instruction is emitted.)
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            asm volatile("" : "+f"(rq[e]), "+f"(rk[e]));
+            if (MODE == 0) asm volatile("" : "+f"(rg[e]));
+        }
+        asm volatile("" : "+f"(rv), "+f"(r1), "+f"(r2));
     };
     auto stage = [&]() {
 #pragma unroll
