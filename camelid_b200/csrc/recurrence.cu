@@ -76,15 +76,18 @@ __global__ void conv_unit_kernel(const float* __restrict__ proj, long ld, const 
             cc[e] = ok[e] ? c : c0;
             acc[e] = 0.f;
         }
+        const int ne = min(8, (c0 + n - base + 31) / 32);  // groups of 32 channels that are there at all (the same for the warp)
         for (int j = 0; j < taps; ++j) {
             const int back = taps - 1 - j;                 // tokens before this one
             if (back > pos) continue;                      // before the sequence's start
             const float* src = back <= inside ? proj + (size_t)(r - back) * ld : st + (size_t)(taps - 1 + inside - back) * channels;
             float x[8], w[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) { x[e] = src[cc[e]]; w[e] = conv_w[(size_t)cc[e] * taps + j]; }
+            for (int e = 0; e < 8; ++e)
+                if (e < ne) { x[e] = src[cc[e]]; w[e] = conv_w[(size_t)cc[e] * taps + j]; }
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[e], x[e], acc[e]);
+            for (int e = 0; e < 8; ++e)
+                if (e < ne) acc[e] = fmaf(w[e], x[e], acc[e]);
         }
         if (update_state && taps > 1) {                    // one row per sequence: drop the oldest input, keep this one
             for (int j = 0; j + 2 < taps; ++j) {

@@ -183,34 +183,56 @@ __global__ void rmsnorm_shift_kernel(float* __restrict__ x, const TW* __restrict
     const int r = blockIdx.x;
     float* xr = x + (size_t)r * hidden;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        float v = xr[c];
-        if (partial) {
-            const float* pp = partial + (size_t)r * hidden + c;
-            for (int s0 = 0; s0 < n_splits; s0 += 8) {
-                float t[8];
+    // two columns of a thread at a time; the row's values and sixteen splits of both are in flight together
+    // (every load unconditional, of a valid place), the adds in split order
+    for (int cb = threadIdx.x; cb < hidden; cb += 2 * blockDim.x) {
+        const int cc[2] = {cb, cb + (int)blockDim.x};
+        const bool in[2] = {true, cc[1] < hidden};
+        float v[2];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float tv = pp[(size_t)min(s0 + i, n_splits - 1) * split_stride];
-                    t[i] = s0 + i < n_splits ? tv : 0.f;
+        for (int j = 0; j < 2; ++j) v[j] = xr[in[j] ? cc[j] : cb];
+        if (partial) {
+            for (int s0 = 0; s0 < n_splits; s0 += 16) {
+                float t[2][16];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const float* pp = partial + (size_t)r * hidden + (in[j] ? cc[j] : cb);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float tv = pp[(size_t)min(s0 + i, n_splits - 1) * split_stride];
+                        t[j][i] = s0 + i < n_splits ? tv : 0.f;
+                    }
                 }
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v += t[i];
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[j] += t[j][i];
             }
-            xr[c] = v;
         }
-        rowbuf[c] = v;
-        ss = fmaf(v, v, ss);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            if (!in[j]) continue;
+            if (partial) xr[cc[j]] = v[j];
+            rowbuf[cc[j]] = v[j];
+            ss = fmaf(v[j], v[j], ss);
+        }
     }
-    ss = block_sum(ss, red);
-    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
     const bool first = row_pos[r] == 0;
     float* st = state + (size_t)seq_slot[row_seq[r]] * hidden;
+    // what the second pass needs besides the row's scale is asked for before the reduction
+    const int c0 = threadIdx.x, c1 = threadIdx.x + blockDim.x;
+    const int a0 = c0 < hidden ? c0 : 0, a1 = c1 < hidden ? c1 : 0;
+    const float w0 = to_f32(w[a0]), w1 = to_f32(w[a1]), m0 = mix[a0], m1 = mix[a1], k0 = st[a0], k1 = st[a1];
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
     T* o = out + (size_t)r * hidden;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float n = to_f32(from_f32<T>(rowbuf[c] * scale * to_f32(w[c])));
-        const float kept = first ? 0.f : st[c];
-        o[c] = from_f32<T>(n + (kept - n) * mix[c]);
+        const float wc = c == c0 ? w0 : (c == c1 ? w1 : to_f32(w[c]));
+        const float mc = c == c0 ? m0 : (c == c1 ? m1 : mix[c]);
+        const float kc = c == c0 ? k0 : (c == c1 ? k1 : st[c]);
+        const float n = to_f32(from_f32<T>(rowbuf[c] * scale * wc));
+        const float kept = first ? 0.f : kc;
+        o[c] = from_f32<T>(n + (kept - n) * mc);
         st[c] = n;
     }
 }
