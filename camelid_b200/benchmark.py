@@ -475,6 +475,28 @@ def model_prefill_flops(lm, tokens: int) -> float:
     return total
 
 
+def _prefill_together(lm, prompts, reps: int = 3, warmup: int = 2) -> dict:
+    """All prompts in one step (the recurrent mixers walk the sequences side by side)."""
+    from .engine.model import StepEntry
+    cache = lm.new_cache(sum(((len(p) + 63) // 64) * 64 for p in prompts), max_slots=len(prompts))
+    times = []
+    for r in range(warmup + reps):
+        slots = [cache.alloc_slot() for _ in prompts]
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        lm.step(cache, [StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        b.record()
+        torch.cuda.synchronize()
+        for s in slots:
+            cache.free_slot(s)
+        if r >= warmup:
+            times.append(a.elapsed_time(b))
+    ms = statistics.median(times)
+    lm.model.drop_graphs(cache)
+    return {"ms": ms, "tokens": sum(len(p) for p in prompts), "value": sum(len(p) for p in prompts) / (ms / 1e3)}
+
+
 def run_fomatar(sizes=("small", "medium"), batch: int = 8, prompt_tokens: int = 512, steps: int = 64, warmup: int = 4,
                 prefill_tokens: int = 2048, dtype: str = "bfloat16") -> dict:
     """Decode steps (timed on the device in the loop ``generate`` runs) and one prefill step of the Fomatar decoder
@@ -495,10 +517,12 @@ def run_fomatar(sizes=("small", "medium"), batch: int = 8, prompt_tokens: int = 
             bytes_step = model_step_bytes(lm, batch, dec["context"])
             pre = measure_prefill(lm, vocab, prefill_tokens, rng)
             flops = model_prefill_flops(lm, prefill_tokens) if label == "fomatar" else prefill_flops(cfg, prefill_tokens)
+            together = _prefill_together(lm, _prompts(rng, batch, prompt_tokens, vocab["vocab_size"]))
             rec[label] = {
                 "decode_tokens_per_s": dec["value"], "decode_ms_per_step": dec["ms_per_step"], "launches_per_step": dec["launches"] / steps,
                 "decode_bytes": bytes_step, "decode_frac_of_copy": bytes_step["total"] / (dec["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"],
                 "prefill_tokens_per_s": pre["value"], "prefill_ms": pre["ms"],
+                "prefill_batch_tokens_per_s": together["value"], "prefill_batch_ms": together["ms"],
                 "prefill_frac_of_gemm": flops / (pre["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12) if dtype == "bfloat16" else None,
                 "clocks": dec["clocks"]}
             del lm
