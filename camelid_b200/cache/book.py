@@ -25,11 +25,28 @@ PAGE = 64
 @dataclass(frozen=True)
 class KVSpec:
     """Keys and values per position: ``window`` None keeps all of them, an integer keeps the
-    last ``window`` positions. ``v_head_dim`` (None: ``head_dim``) is the size of a value."""
+    last ``window`` positions. ``v_head_dim`` (None: ``head_dim``) is the size of a value.
+    ``chunk``: queries see only the keys of their own block of ``chunk`` positions (blocks counted
+    from position 0), so the positions before the running block are never read again."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
+    chunk: Optional[int] = None
+
+    @property
+    def forgets(self) -> bool:
+        """Whether old positions stop being visible (and their pages are given back)."""
+        return self.window is not None or self.chunk is not None
+
+    def first_visible(self, position: int) -> int:
+        """The oldest position a query at ``position`` or later can still see."""
+        first = 0
+        if self.window is not None:
+            first = max(first, position - self.window + 1)
+        if self.chunk is not None:
+            first = max(first, position - position % self.chunk)
+        return first
 
     @property
     def value_dim(self) -> int:
@@ -133,10 +150,7 @@ class CacheBook:
     # ---- pages ----
     def _first_needed_block(self, g: int, length_before: int) -> int:
         """First block a query at a position >= length_before can still see."""
-        w = self.kv_specs[g].window
-        if w is None:
-            return 0
-        return max(0, length_before - w + 1) // PAGE
+        return self.kv_specs[g].first_visible(length_before) // PAGE
 
     def pages_needed(self, slot: int, new_length: int) -> list:
         """Pages each group has to add so that positions < new_length have storage."""
@@ -197,7 +211,7 @@ class CacheBook:
         if not 0 <= length <= self.length[slot]:
             raise CacheError(f"slot {slot}: cannot truncate from {self.length[slot]} to {length}")
         for g in range(len(self.pools)):
-            if self.kv_specs[g].window is not None and length < self.length[slot]:
+            if self.kv_specs[g].forgets and length < self.length[slot]:
                 first = self._first_needed_block(g, length)
                 if any(p < 0 for p in self.pages[g][slot][first:(length + PAGE - 1) // PAGE]):
                     raise CacheError(f"slot {slot}: group {g} has already given back positions before {length}")

@@ -27,13 +27,18 @@ class LayerSpec:
     """One layer: the arrangement of its parts (``prenorm``: x + mixer(norm(x)), then
     r + ffn(norm(r))) and the parts themselves. Layers of one model may differ. A layer
     without ``ffn`` (and ``norm2``) has only the first sublayer; ``shift`` names a part that
-    stands between the first norm and the mixer (a token shift)."""
+    stands between the first norm and the mixer (a token shift). The ``sandwich`` arrangement
+    also norms every sublayer's output before it is added, x + scale * post_norm(sublayer(norm(x))),
+    with ``post_norm1`` / ``post_norm2`` and ``residual_scale``."""
     arrangement: str
     norm1: PartSpec
     mixer: PartSpec
     norm2: Optional[PartSpec] = None
     ffn: Optional[PartSpec] = None
     shift: Optional[PartSpec] = None
+    post_norm1: Optional[PartSpec] = None
+    post_norm2: Optional[PartSpec] = None
+    residual_scale: float = 1.0
 
 
 @dataclass(frozen=True)

@@ -128,3 +128,11 @@ def _register_fomatar():
 
 
 _register_fomatar()
+
+
+def _register_zulozen():
+    from .zulozen import ZulozenConfig, zulozen_plan
+    register_architecture("Zulozen", ZulozenConfig.from_dict, zulozen_plan)
+
+
+_register_zulozen()

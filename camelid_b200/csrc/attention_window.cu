@@ -4,6 +4,12 @@
 //
 //   score(i, j) = (q_i . k_j) scale - r1[head] ln(1 + r2[head] (i - j)),   0 <= i - j < window
 //
+// Besides the window, a query may be held to the keys of its own block of `chunk` positions (blocks
+// counted from position 0 of the sequence); the softmax denominator may hold one more term
+// exp(sink[head]) that has no key and no value; the gate may be one number per head. A second
+// preparing kernel normalises q and k over their whole projections (all heads at once) and rotates
+// pairs of channels by the position (pairs of neighbours, or of the two halves of the rotated part).
+//
 // Two kernels. The first normalises q and k (weight per channel, shared by the heads), keeps
 // q in the compute type and writes k and v into their pages. The second gives a block to
 // every (row, head): lanes take keys for the scores (all in float), then columns of the
@@ -85,6 +91,99 @@ extern "C" int cml_qk_norm_kv_write(const float* proj, long ld, const void* q_w,
     return CML_ERR_BAD_DTYPE;
 }
 
+// The same job for mixers that rotate: proj [rows, ld] float holds q, k, v as above. norm_mode 0: q and k as
+// they are; 1: RMS norm per head, weights of D channels shared by the heads; 2: RMS norm over the whole q
+// projection (heads x D channels at once) and the whole k projection, weights of those sizes. Then the first
+// rot_dim channels of every q and k head are rotated by angle = position * inv_freq[i] (float), pairing 1:
+// channels (2i, 2i + 1); pairing 0: channels (i, i + rot_dim / 2). One block per row.
+template <typename T, typename TW>
+__global__ void __launch_bounds__(256) qkv_prepare_kernel(const float* __restrict__ proj, long ld, const TW* __restrict__ q_w,
+                                   const TW* __restrict__ k_w, int norm_mode, float eps, const float* __restrict__ inv_freq,
+                                   int rot_dim, int pairing, const int* __restrict__ row_seq, const int* __restrict__ row_pos,
+                                   const int* __restrict__ table, int max_blocks, T* __restrict__ q_out, T* __restrict__ k_pages,
+                                   T* __restrict__ v_pages, int heads, int kv_heads, int D, int Dv) {
+    __shared__ float red[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const float* x = proj + (size_t)r * ld;
+    const int qw = heads * D, kw = kv_heads * D, vw = kv_heads * Dv;
+    const int pos = row_pos[r];
+    const int page = table[(size_t)row_seq[r] * max_blocks + pos / CML_PAGE];
+    float q_scale = 1.0f, k_scale = 1.0f;
+    if (norm_mode == 2) {
+        float sq = 0.f, sk = 0.f;
+        for (int c = threadIdx.x; c < qw; c += blockDim.x) sq = fmaf(x[c], x[c], sq);
+        for (int c = threadIdx.x; c < kw; c += blockDim.x) sk = fmaf(x[qw + c], x[qw + c], sk);
+        q_scale = 1.0f / sqrtf(block_sum(sq, red) / (float)qw + eps);
+        __syncthreads();
+        k_scale = 1.0f / sqrtf(block_sum(sk, red) / (float)kw + eps);
+        __syncthreads();
+    }
+    const int half = rot_dim / 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    // q and k heads: a warp per head at a time; its lanes take pairs of channels
+    for (int u0 = 0; u0 < heads + kv_heads; u0 += nwarps) {
+        const int u = u0 + warp;
+        if (u < heads + kv_heads) {
+            const bool is_q = u < heads;
+            const int hd = is_q ? u : u - heads;
+            const float* xh = x + (is_q ? 0 : qw) + hd * D;
+            float sc = is_q ? q_scale : k_scale;
+            if (norm_mode == 1) {
+                float ss = 0.f;
+                for (int c = lane; c < D; c += 32) ss = fmaf(xh[c], xh[c], ss);
+                sc = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
+            }
+            const TW* w = is_q ? q_w : k_w;
+            const int woff = norm_mode == 2 ? hd * D : 0;
+            T* o = is_q ? q_out + ((size_t)r * heads + hd) * D
+                        : (page >= 0 ? k_pages + (((size_t)page * kv_heads + hd) * CML_PAGE + pos % CML_PAGE) * D : nullptr);
+            if (o != nullptr) {
+                for (int i = lane; i < half; i += 32) {
+                    const int c0 = pairing ? 2 * i : i, c1 = pairing ? 2 * i + 1 : i + half;
+                    float a = xh[c0], b = xh[c1];
+                    if (norm_mode) { a = a * sc * to_f32(w[woff + c0]); b = b * sc * to_f32(w[woff + c1]); }
+                    float sn, cs;
+                    sincosf((float)pos * inv_freq[i], &sn, &cs);
+                    o[c0] = from_f32<T>(a * cs - b * sn);
+                    o[c1] = from_f32<T>(b * cs + a * sn);
+                }
+                for (int c = 2 * half + lane; c < D; c += 32)
+                    o[c] = from_f32<T>(norm_mode ? xh[c] * sc * to_f32(w[woff + c]) : xh[c]);
+            }
+        }
+    }
+    if (page >= 0) {
+        for (int c = threadIdx.x; c < vw; c += blockDim.x) {
+            const int g = c / Dv, e = c - g * Dv;
+            v_pages[(((size_t)page * kv_heads + g) * CML_PAGE + pos % CML_PAGE) * Dv + e] = from_f32<T>(x[qw + kw + c]);
+        }
+    }
+}
+
+extern "C" int cml_qkv_prepare(const float* proj, long ld, const void* q_w, const void* k_w, int w_dtype, int norm_mode, float eps,
+                               const float* inv_freq, int rot_dim, int pairing, const int* row_seq, const int* row_pos,
+                               const int* table, int max_blocks, void* q_out, void* k_pages, void* v_pages, int dtype, int rows,
+                               int heads, int kv_heads, int D, int Dv, void* stream) {
+    if (rows <= 0) return 0;
+    if (rot_dim < 0 || rot_dim > D || (rot_dim & 1) || norm_mode < 0 || norm_mode > 2) return CML_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+#define QP_CASE(T_, TW_, D_, DW_)                                                                                          \
+    if (dtype == D_ && w_dtype == DW_) {                                                                                   \
+        launch_pdl(qkv_prepare_kernel<T_, TW_>, dim3(rows), dim3(256), 0, s, proj, ld, (const TW_*)q_w, (const TW_*)k_w,   \
+                   norm_mode, eps, inv_freq, rot_dim, pairing, row_seq, row_pos, table, max_blocks, (T_*)q_out,            \
+                   (T_*)k_pages, (T_*)v_pages, heads, kv_heads, D, Dv);                                                    \
+        return cml_launch_status();                                                                                        \
+    }
+    QP_CASE(float, float, CML_DTYPE_F32, CML_DTYPE_F32)
+    QP_CASE(bf16, bf16, CML_DTYPE_BF16, CML_DTYPE_BF16)
+    QP_CASE(bf16, float, CML_DTYPE_BF16, CML_DTYPE_F32)
+    QP_CASE(float, bf16, CML_DTYPE_F32, CML_DTYPE_BF16)
+#undef QP_CASE
+    return CML_ERR_BAD_DTYPE;
+}
+
 // q [rows, heads x D]; out [rows, heads x Dv] = softmax(...) V, times sigmoid(gate) where
 // gate (float [rows, ldg], at column gate_col) is given. window <= 0: all keys. r1, r2 float
 // [heads] or null (no penalty).
@@ -125,7 +224,8 @@ __global__ void __launch_bounds__(512, 1) window_attention_kernel(const T* __res
                                         const int* __restrict__ table, int max_blocks, const int* __restrict__ row_seq,
                                         const int* __restrict__ row_pos, const float* __restrict__ r1,
                                         const float* __restrict__ r2, const float* __restrict__ gate, long ldg, int gate_col,
-                                        T* __restrict__ out, int heads, int kv_heads, int D, int Dv, int window, float scale) {
+                                        T* __restrict__ out, int heads, int kv_heads, int D, int Dv, int window, float scale,
+                                        int chunk, const float* __restrict__ sink, int gate_per_head) {
     extern __shared__ __align__(16) float aw_sh[];
     pdl_wait();
     pdl_launch_dependents();
@@ -135,7 +235,8 @@ __global__ void __launch_bounds__(512, 1) window_attention_kernel(const T* __res
     float* part = aw_sh + ((D + 3) & ~3) + warp * (Dv + 2);
     // what the first round needs besides the query is asked for before the query is staged
     const int i = row_pos[r];
-    const int lo = window > 0 ? max(0, i - window + 1) : 0;
+    int lo = window > 0 ? max(0, i - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, i - i % chunk);             // the first position of the row's own block
     const int rounds = (i - lo) / 32 + 1;
     const int per_warp = (rounds + nw - 1) / nw;
     const int j_first = lo + 32 * warp * per_warp, j_end = min(i + 1, j_first + 32 * per_warp);
@@ -248,40 +349,49 @@ __global__ void __launch_bounds__(512, 1) window_attention_kernel(const T* __res
     const float* parts = aw_sh + ((D + 3) & ~3);
     float top = -INFINITY;
     for (int w = 0; w < nw; ++w) top = fmaxf(top, parts[w * (Dv + 2)]);
+    const float snk = sink ? sink[hd] : -INFINITY;              // one more term of the denominator, without a value
+    top = fmaxf(top, snk);
     float total = 0.f;
     for (int w = 0; w < nw; ++w) {
         const float mw = parts[w * (Dv + 2)];
         if (mw != -INFINITY) total += parts[w * (Dv + 2) + 1] * expf(mw - top);
     }
+    if (sink) total += expf(snk - top);
     const float inv = 1.0f / total;
     T* o = out + ((size_t)r * heads + hd) * Dv;
-    const float* gt = gate ? gate + (size_t)r * ldg + gate_col + hd * Dv : nullptr;
+    const float* gt = gate ? gate + (size_t)r * ldg + gate_col + (gate_per_head ? hd : hd * Dv) : nullptr;
+    const int gstep = gate_per_head ? 0 : 1;
     for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
         float sum = 0.f;
         for (int w = 0; w < nw; ++w) {
             const float mw = parts[w * (Dv + 2)];
             if (mw != -INFINITY) sum += parts[w * (Dv + 2) + 2 + c] * expf(mw - top);
         }
-        o[c] = from_f32<T>(sum * inv * (gt ? sigmoid_w(gt[c]) : 1.0f));
+        o[c] = from_f32<T>(sum * inv * (gt ? sigmoid_w(gt[c * gstep]) : 1.0f));
     }
 }
 
 extern "C" int cml_window_attention(const void* q, const void* k_pages, const void* v_pages, int dtype, const int* table,
                                     int max_blocks, const int* row_seq, const int* row_pos, const float* r1, const float* r2,
                                     const float* gate, long ldg, int gate_col, void* out, int rows, int heads, int kv_heads,
-                                    int D, int Dv, int window, float scale, void* stream) {
+                                    int D, int Dv, int window, float scale, int chunk, const float* sink, int gate_per_head,
+                                    void* stream) {
     if (rows <= 0) return 0;
     if (Dv > 32 * AW_MAX_VREGS || D < 1 || heads % kv_heads) return CML_ERR_BAD_SIZE;
     // warps per (row, head): one per round of 32 keys of the window, at most 16 (8 without a window); fixed by
     // the window alone, so a row's sums do not depend on the step it came in
-    const int nw = window > 0 ? ((window + 31) / 32 < 16 ? (window + 31) / 32 : 16) : 8;
+    // (or by the block of positions, whichever lets a query see fewer keys)
+    int span = window > 0 ? window : 0;
+    if (chunk > 0 && (span == 0 || chunk < span)) span = chunk;
+    const int nw = span > 0 ? ((span + 31) / 32 < 16 ? (span + 31) / 32 : 16) : 8;
     dim3 grid((unsigned)((long)rows * heads));
     const size_t smem = (size_t)(((D + 3) & ~3) + nw * (Dv + 2)) * sizeof(float);
     if (smem > 48 * 1024 || (long)rows * heads > 0x7fffffffL) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
 #define AW_CASE(T_, NV_)                                                                                                    \
     launch_pdl(window_attention_kernel<T_, NV_>, grid, dim3(32 * nw), smem, s, (const T_*)q, (const T_*)k_pages, (const T_*)v_pages, \
-               table, max_blocks, row_seq, row_pos, r1, r2, gate, ldg, gate_col, (T_*)out, heads, kv_heads, D, Dv, window, scale)
+               table, max_blocks, row_seq, row_pos, r1, r2, gate, ldg, gate_col, (T_*)out, heads, kv_heads, D, Dv, window, scale, \
+               chunk, sink, gate_per_head)
 #define AW_SIZES(T_)                                                                                                        \
     if (Dv <= 32) AW_CASE(T_, 1); else if (Dv <= 64) AW_CASE(T_, 2); else if (Dv <= 128) AW_CASE(T_, 4); else AW_CASE(T_, 8)
     if (dtype == CML_DTYPE_F32) { AW_SIZES(float); }

@@ -90,11 +90,12 @@ _SIGNATURES = {
                                          c_int, c_int, c_int, c_float, c_void_p, c_int, c_long, c_void_p],
     ("token_ops", "cml_add_rows_vec"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     ("token_ops", "cml_gelu_tanh"): [c_void_p, c_int, c_long, c_void_p],
-    ("token_ops", "cml_act_from_partials"): [c_void_p, c_int, c_long, c_void_p, c_int, c_long, c_int, c_void_p],
+    ("token_ops", "cml_act_from_partials"): [c_void_p, c_int, c_long, c_void_p, c_int, c_long, c_int, c_void_p, c_int, c_void_p],
+    ("token_ops", "cml_bias_act"): [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
     ("token_ops", "cml_gate_rows"): [c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p],
     ("token_ops", "cml_softcap"): [c_void_p, c_long, c_float, c_void_p],
-    ("token_ops", "cml_norm_combine"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_float,
-                                        c_float, c_void_p],
+    ("token_ops", "cml_norm_combine"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                                        c_float, c_float, c_void_p],
     ("recurrence", "cml_conv_unit"): [c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_long, c_void_p, c_void_p,
                                       c_void_p, c_void_p],
@@ -111,7 +112,18 @@ _SIGNATURES = {
                                                    c_int, c_int, c_int, c_int, c_void_p],
     ("attention_window", "cml_window_attention"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                                    c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int,
-                                                   c_int, c_int, c_int, c_float, c_void_p],
+                                                   c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p],
+    ("attention_window", "cml_qkv_prepare"): [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int,
+                                              c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                              c_int, c_int, c_int, c_int, c_void_p],
+    ("experts", "cml_route_topk"): [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ("experts", "cml_expert_plan"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    ("experts", "cml_expert_gather"): [c_void_p, c_int, c_long, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                       c_int, c_void_p, c_void_p, c_void_p],
+    ("experts", "cml_expert_gemm"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                     c_void_p, c_void_p],
+    ("experts", "cml_expert_combine"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_long, c_void_p, c_int,
+                                        c_int, c_void_p],
     ("random_fill", "cml_random_fill"): [c_void_p, c_int, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_ulonglong,
                                          ctypes.c_double, ctypes.c_double, c_void_p],
 }
@@ -396,13 +408,29 @@ def gelu_tanh_(x: torch.Tensor):
     _check(_fn("token_ops", "cml_gelu_tanh")(_p(x), dtype_code(x.dtype), x.numel(), _stream()), "gelu_tanh")
 
 
-def act_from_partials(part: torch.Tensor, out: torch.Tensor, gelu: bool):
-    """out = act(sum over splits of part) in the compute type; part float32 [splits, rows, n], act GELU (tanh form) or none."""
-    _dev(part, out)
+ACT_NONE, ACT_GELU_TANH, ACT_RELU_SQUARED = 0, 1, 2
+ACTIVATIONS = {None: ACT_NONE, "none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "relu_squared": ACT_RELU_SQUARED}
+
+
+def act_from_partials(part: torch.Tensor, out: torch.Tensor, gelu: bool = False, act: int | None = None, bias=None):
+    """out = act(sum over splits of part + bias) in the compute type; part float32 [splits, rows, n]; ``act`` one of
+    the ACT_* codes (``gelu``: the tanh form of GELU); ``bias`` float32 [n] or None."""
+    _dev(part, out, bias)
     assert part.dtype == torch.float32 and part.dim() == 3 and part.is_contiguous() and out.is_contiguous()
     assert tuple(out.shape) == tuple(part.shape[1:])
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == out.shape[-1] and bias.is_contiguous())
+    code = act if act is not None else (ACT_GELU_TANH if gelu else ACT_NONE)
     _check(_fn("token_ops", "cml_act_from_partials")(_p(part), part.shape[0], part.stride(0), _p(out), dtype_code(out.dtype),
-                                                     out.numel(), 1 if gelu else 0, _stream()), "act_from_partials")
+                                                     out.numel(), code, _p(bias), out.shape[-1], _stream()), "act_from_partials")
+
+
+def bias_act_(x: torch.Tensor, bias, act: int):
+    """x[r, c] = act(x[r, c] + bias[c]) in place; ``bias`` float32 [columns] or None; ``act`` one of the ACT_* codes."""
+    _dev(x, bias)
+    assert x.dim() == 2 and x.is_contiguous()
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == x.shape[1] and bias.is_contiguous())
+    _check(_fn("token_ops", "cml_bias_act")(_p(x), dtype_code(x.dtype), _p(bias), x.shape[0], x.shape[1], int(act), _stream()),
+           "bias_act")
 
 
 def gate_rows_(x: torch.Tensor, gate: torch.Tensor, gate_col: int):
@@ -421,13 +449,19 @@ def softcap_(x: torch.Tensor, cap: float):
     _check(_fn("token_ops", "cml_softcap")(_p(x), x.numel(), float(cap), _stream()), "softcap")
 
 
-def norm_combine(branches: list, residual: torch.Tensor, eps: float, coef: float):
-    """residual[r] += coef * sum of rmsnorm(y[r]) * w over ``branches`` = [(y, w)], y float32
-    [rows, hidden] or [splits, rows, hidden] (splits summed first), w [hidden]."""
+def norm_combine(branches: list, residual: torch.Tensor, eps: float, coef: float, biases: list | None = None):
+    """residual[r] += coef * sum of rmsnorm(y[r] + bias) * w over ``branches`` = [(y, w)], y float32
+    [rows, hidden] or [splits, rows, hidden] (splits summed first), w [hidden]; ``biases``: per branch a
+    float32 [hidden] vector or None."""
     rows, hidden = residual.shape
     assert 1 <= len(branches) <= 4 and residual.dtype == torch.float32 and residual.is_contiguous()
     n = len(branches)
-    ys, ws, splits, strides = (c_void_p * n)(), (c_void_p * n)(), (c_int * n)(), (c_long * n)()
+    ys, ws, bs, splits, strides = (c_void_p * n)(), (c_void_p * n)(), (c_void_p * n)(), (c_int * n)(), (c_long * n)()
+    for i, b in enumerate(biases or [None] * n):
+        if b is not None:
+            _dev(b)
+            assert b.dtype == torch.float32 and b.numel() == hidden and b.is_contiguous()
+        bs[i] = _p(b)
     for i, (y, w) in enumerate(branches):
         _dev(y, w)
         if y.dim() == 2:
@@ -435,7 +469,7 @@ def norm_combine(branches: list, residual: torch.Tensor, eps: float, coef: float
         assert y.dtype == torch.float32 and y.shape[1:] == (rows, hidden) and y.stride(2) == 1 and y.stride(1) == hidden
         assert w.numel() == hidden and w.is_contiguous() and w.dtype == branches[0][1].dtype
         ys[i], ws[i], splits[i], strides[i] = y.data_ptr(), w.data_ptr(), y.shape[0], y.stride(0)
-    _check(_fn("token_ops", "cml_norm_combine")(ys, ws, splits, strides, n, dtype_code(branches[0][1].dtype), _p(residual),
+    _check(_fn("token_ops", "cml_norm_combine")(ys, ws, bs, splits, strides, n, dtype_code(branches[0][1].dtype), _p(residual),
                                                 rows, hidden, float(eps), float(coef), _stream()), "norm_combine")
 
 
@@ -549,10 +583,14 @@ def qk_norm_kv_write(proj: torch.Tensor, q_w, k_w, eps: float, row_seq, row_pos,
 
 
 def window_attention(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate, gate_col: int, out, heads: int,
-                     kv_heads: int, key_dim: int, value_dim: int, window: int, scale: float):
+                     kv_heads: int, key_dim: int, value_dim: int, window: int, scale: float, chunk: int = 0, sink=None,
+                     gate_per_head: bool = False):
     """out[r, head] = softmax_j((q . k_j) scale - r1 ln(1 + r2 (i - j))) V over the last ``window`` keys
-    (0: all), times sigmoid(gate[r, gate_col + ...]) where ``gate`` (float32) is given."""
-    _dev(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate, out)
+    (0: all) and, with ``chunk``, only those of the row's own block of ``chunk`` positions; ``sink`` (float32
+    [heads]): one more term exp(sink) in the denominator; times sigmoid(gate[r, gate_col + ...]) where ``gate``
+    (float32) is given: a number per channel of every head, or per head."""
+    _dev(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate, out, sink)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == heads and sink.is_contiguous())
     rows = q.shape[0]
     assert q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype == k_pages.dtype == v_pages.dtype
     assert out.shape == (rows, heads * value_dim) and q.shape[1] == heads * key_dim
@@ -563,7 +601,96 @@ def window_attention(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate,
     _check(_fn("attention_window", "cml_window_attention")(
         _p(q), _p(k_pages), _p(v_pages), dtype_code(q.dtype), _p(table), table.shape[1], _p(row_seq), _p(row_pos), _p(r1),
         _p(r2), _p(gate), gate.stride(0) if gate is not None else 0, gate_col, _p(out), rows, heads, kv_heads, key_dim,
-        value_dim, int(window or 0), float(scale), _stream()), "window_attention")
+        value_dim, int(window or 0), float(scale), int(chunk or 0), _p(sink), 1 if gate_per_head else 0, _stream()),
+        "window_attention")
+
+
+def qkv_prepare(proj: torch.Tensor, q_w, k_w, norm_mode: int, eps: float, inv_freq, rotary_dim: int, interleaved: bool,
+                row_seq, row_pos, table, q_out, k_pages, v_pages, heads: int, kv_heads: int, key_dim: int, value_dim: int):
+    """From ``proj`` (float32 rows: q, k, v): RMS norm of q and k (``norm_mode`` 0 none, 1 per head with weights
+    [key_dim], 2 over the whole projection with weights [heads * key_dim] and [kv_heads * key_dim]), then the
+    first ``rotary_dim`` channels of every head rotated by position * inv_freq (pairs of neighbours if
+    ``interleaved``, else of the two halves); q to ``q_out``, k and v into their pages, in the compute type."""
+    _dev(proj, q_w, k_w, inv_freq, row_seq, row_pos, table, q_out, k_pages, v_pages)
+    rows = q_out.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1
+    assert proj.shape[1] >= heads * key_dim + kv_heads * (key_dim + value_dim)
+    assert q_out.is_contiguous() and q_out.shape[1] == heads * key_dim and k_pages.dtype == q_out.dtype == v_pages.dtype
+    assert k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert k_pages.shape[1:] == (kv_heads, PAGE, key_dim) and v_pages.shape[1:] == (kv_heads, PAGE, value_dim)
+    if norm_mode:
+        per = key_dim if norm_mode == 1 else heads * key_dim
+        assert q_w.numel() == per and k_w.numel() == (key_dim if norm_mode == 1 else kv_heads * key_dim) and q_w.dtype == k_w.dtype
+    if rotary_dim:
+        assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2
+    _check(_fn("attention_window", "cml_qkv_prepare")(
+        _p(proj), proj.stride(0), _p(q_w), _p(k_w), dtype_code(q_w.dtype) if norm_mode else dtype_code(q_out.dtype), int(norm_mode),
+        float(eps), _p(inv_freq), int(rotary_dim), 1 if interleaved else 0, _p(row_seq), _p(row_pos), _p(table), table.shape[1],
+        _p(q_out), _p(k_pages), _p(v_pages), dtype_code(q_out.dtype), rows, heads, kv_heads, key_dim, value_dim, _stream()),
+        "qkv_prepare")
+
+
+# ---------------------------------------------------------------------------------------
+# routed feed-forwards
+
+def route_topk(logits: torch.Tensor, top: int, softmax: bool, renorm: bool, ids: torch.Tensor, wts: torch.Tensor):
+    """The ``top`` largest logits of every row: their expert ids and weights (sigmoid of the logit, or its softmax
+    over all experts; ``renorm``: divided by the chosen weights' sum). logits float32 [rows, experts]."""
+    _dev(logits, ids, wts)
+    rows, experts = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and ids.dtype == torch.int32 and wts.dtype == torch.float32
+    assert ids.numel() == rows * top == wts.numel() and ids.is_contiguous() and wts.is_contiguous()
+    _check(_fn("experts", "cml_route_topk")(_p(logits), logits.stride(0), rows, experts, int(top), 1 if softmax else 0,
+                                            1 if renorm else 0, _p(ids), _p(wts), _stream()), "route_topk")
+
+
+def expert_plan(ids: torch.Tensor, experts: int, rank, counts, offsets, tile_first):
+    """Orders the (row, choice) pairs by expert: ``rank`` of each pair among its expert's, ``counts`` per expert,
+    ``offsets`` [experts + 1] and the first tile of every expert's stretch ``tile_first`` [experts + 1]."""
+    _dev(ids, rank, counts, offsets, tile_first)
+    assert all(t.dtype == torch.int32 and t.is_contiguous() for t in (ids, rank, counts, offsets, tile_first))
+    assert rank.numel() == ids.numel() and counts.numel() >= experts and offsets.numel() > experts and tile_first.numel() > experts
+    _check(_fn("experts", "cml_expert_plan")(_p(ids), ids.numel(), experts, _p(rank), _p(counts), _p(offsets), _p(tile_first),
+                                             _stream()), "expert_plan", launches=2)
+
+
+def expert_gather(x: torch.Tensor, ids, wts, rank, offsets, top: int, scale_input: bool, xs: torch.Tensor, pos_of_pair):
+    """xs[offsets[expert] + rank] = x[row] (times the pair's weight if ``scale_input``); ``pos_of_pair`` keeps the place."""
+    _dev(x, ids, wts, rank, offsets, xs, pos_of_pair)
+    pairs = ids.numel()
+    assert x.stride(1) == 1 and xs.is_contiguous() and xs.shape == (pairs, x.shape[1]) and xs.dtype == x.dtype
+    _check(_fn("experts", "cml_expert_gather")(_p(x), dtype_code(x.dtype), x.stride(0), x.shape[1], _p(ids), _p(wts), _p(rank),
+                                               _p(offsets), pairs, int(top), 1 if scale_input else 0, _p(xs), _p(pos_of_pair),
+                                               _stream()), "expert_gather")
+
+
+def expert_gemm(a: torch.Tensor, w: torch.Tensor, w2, out: torch.Tensor, offsets, tile_first):
+    """Per expert e: out[stretch e] = a[stretch e] @ w[e].T (float32), or with ``w2``
+    silu(a @ w[e].T) * (a @ w2[e].T) in the compute type. w [experts, n, k]; the stretches are ``offsets``."""
+    _dev(a, w, w2, out, offsets, tile_first)
+    pairs, k = a.shape
+    experts, n, k2 = w.shape
+    assert k == k2 and a.is_contiguous() and w.is_contiguous() and a.dtype == w.dtype and out.is_contiguous()
+    assert out.shape == (pairs, n) and out.dtype == (a.dtype if w2 is not None else torch.float32)
+    assert w2 is None or (w2.shape == w.shape and w2.is_contiguous() and w2.dtype == w.dtype)
+    _check(_fn("experts", "cml_expert_gemm")(_p(a), _p(w), _p(w2), dtype_code(a.dtype), _p(out), pairs, n, k, experts,
+                                             _p(offsets), _p(tile_first), _stream()), "expert_gemm")
+
+
+def expert_combine(y: torch.Tensor, pos_of_pair, wts, top: int, scale_output: bool, shared, out: torch.Tensor):
+    """out[row] = shared[row] + sum over the row's choices of y[place of the pair] (times its weight if
+    ``scale_output``); ``shared`` float32 [rows, hidden] or [splits, rows, hidden] or None."""
+    _dev(y, pos_of_pair, wts, shared, out)
+    rows, hidden = out.shape
+    assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == (rows * top, hidden) and out.is_contiguous()
+    splits, stride = 0, 0
+    if shared is not None:
+        if shared.dim() == 2:
+            shared = shared.unsqueeze(0)
+        assert shared.dtype == torch.float32 and shared.shape[1:] == (rows, hidden) and shared.stride(2) == 1 and shared.stride(1) == hidden
+        splits, stride = shared.shape[0], shared.stride(0)
+    _check(_fn("experts", "cml_expert_combine")(_p(y), _p(pos_of_pair), _p(wts), int(top), 1 if scale_output else 0, _p(shared),
+                                                splits, stride, _p(out), rows, hidden, _stream()), "expert_combine")
 
 
 TC_STORE, TC_STORE_F32, TC_ADD_F32, TC_SWIGLU, TC_T_PARTIAL, TC_T_SWIGLU = 0, 1, 2, 3, 4, 5

@@ -310,11 +310,40 @@ extern "C" int cml_gelu_tanh(void* x, int dtype, long n, void* stream) {
     return cml_launch_status();
 }
 
-// out[i] = act(sum over splits of part[split][i]) in the compute type: the split sums of a product of few
-// rows, added in split order, through GELU (act 1) or as they are (act 0).
+// The activations of the dense feed-forwards: 0 none, 1 GELU (tanh form), 2 the square of ReLU.
+__device__ __forceinline__ float apply_act(float v, int act) {
+    if (act == 1) return gelu_tanh_f(v);
+    if (act == 2) { const float p = fmaxf(v, 0.f); return p * p; }
+    return v;
+}
+
+// x[r, c] = act(x[r, c] + bias[c]) in place (bias float or null).
+template <typename T>
+__global__ void bias_act_kernel(T* __restrict__ x, const float* __restrict__ bias, long n, int width, int act) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const float b = bias ? bias[i % width] : 0.f;
+        x[i] = from_f32<T>(apply_act(to_f32(x[i]) + b, act));
+    }
+}
+
+extern "C" int cml_bias_act(void* x, int dtype, const float* bias, int rows, int width, int act, void* stream) {
+    const long n = (long)rows * width;
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int grid = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+    if (dtype == CML_DTYPE_F32) launch_pdl(bias_act_kernel<float>, dim3(grid), dim3(256), 0, s, (float*)x, bias, n, width, act);
+    else if (dtype == CML_DTYPE_BF16) launch_pdl(bias_act_kernel<bf16>, dim3(grid), dim3(256), 0, s, (bf16*)x, bias, n, width, act);
+    else return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}
+
+// out[i] = act(sum over splits of part[split][i] + bias[column]) in the compute type: the split sums of a product
+// of few rows, added in split order, then the bias (float [width] or null), then the activation (codes above).
 template <typename T>
 __global__ void act_from_partials_kernel(const float* __restrict__ part, int n_splits, size_t stride, T* __restrict__ out,
-                                         long n, int act) {
+                                         long n, int act, const float* __restrict__ bias, int width) {
     pdl_wait();
     pdl_launch_dependents();
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
@@ -329,20 +358,21 @@ __global__ void act_from_partials_kernel(const float* __restrict__ part, int n_s
 #pragma unroll
             for (int k = 0; k < 8; ++k) v += t[k];
         }
-        out[i] = from_f32<T>(act == 1 ? gelu_tanh_f(v) : v);
+        if (bias) v += bias[i % width];
+        out[i] = from_f32<T>(apply_act(v, act));
     }
 }
 
 extern "C" int cml_act_from_partials(const float* part, int n_splits, long stride, void* out, int dtype, long n, int act,
-                                     void* stream) {
+                                     const float* bias, int width, void* stream) {
     if (n <= 0) return 0;
     if (n_splits < 1) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const int grid = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
     if (dtype == CML_DTYPE_F32)
-        launch_pdl(act_from_partials_kernel<float>, dim3(grid), dim3(256), 0, s, part, n_splits, (size_t)stride, (float*)out, n, act);
+        launch_pdl(act_from_partials_kernel<float>, dim3(grid), dim3(256), 0, s, part, n_splits, (size_t)stride, (float*)out, n, act, bias, width);
     else if (dtype == CML_DTYPE_BF16)
-        launch_pdl(act_from_partials_kernel<bf16>, dim3(grid), dim3(256), 0, s, part, n_splits, (size_t)stride, (bf16*)out, n, act);
+        launch_pdl(act_from_partials_kernel<bf16>, dim3(grid), dim3(256), 0, s, part, n_splits, (size_t)stride, (bf16*)out, n, act, bias, width);
     else
         return CML_ERR_BAD_DTYPE;
     return cml_launch_status();
@@ -388,12 +418,13 @@ extern "C" int cml_softcap(float* x, long n, float cap, void* stream) {
 }
 
 // ------------------------------------------------------------------------------------
-// residual[r] += coef * sum over branches b of rmsnorm(y_b[r]) * w_b. Each y_b is a float
+// residual[r] += coef * sum over branches b of rmsnorm(y_b[r] + bias_b) * w_b. Each y_b is a float
 // matrix [splits_b, rows, hidden] whose splits are summed first, in index order. One block
 // per row; the rows of all branches are kept in shared memory between the two passes.
 struct CombineBranches {
     const float* y[4];
     const void* w[4];
+    const float* bias[4];       // added to the branch's summed row before its norm (null: none)
     int splits[4];
     long split_stride[4];
     int n;
@@ -443,6 +474,7 @@ __global__ void __launch_bounds__(512) norm_combine_kernel(CombineBranches br, f
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             if (b >= br.n) continue;
+            if (br.bias[b]) v[b] += br.bias[b][c];
             rowbuf[(size_t)b * hidden + c] = v[b];
             ss[b] = fmaf(v[b], v[b], ss[b]);
         }
@@ -465,8 +497,8 @@ __global__ void __launch_bounds__(512) norm_combine_kernel(CombineBranches br, f
     }
 }
 
-extern "C" int cml_norm_combine(const float* const* y, const void* const* w, const int* splits, const long* split_stride,
-                                int n_branches, int w_dtype, float* residual, int rows, int hidden, float eps, float coef,
+extern "C" int cml_norm_combine(const float* const* y, const void* const* w, const float* const* bias, const int* splits,
+                                const long* split_stride, int n_branches, int w_dtype, float* residual, int rows, int hidden, float eps, float coef,
                                 void* stream) {
     if (rows <= 0) return 0;
     if (n_branches < 1 || n_branches > 4) return CML_ERR_BAD_SIZE;
@@ -475,6 +507,7 @@ extern "C" int cml_norm_combine(const float* const* y, const void* const* w, con
     for (int b = 0; b < 4; ++b) {
         br.y[b] = b < n_branches ? y[b] : nullptr;
         br.w[b] = b < n_branches ? w[b] : nullptr;
+        br.bias[b] = (b < n_branches && bias) ? bias[b] : nullptr;
         br.splits[b] = b < n_branches ? splits[b] : 0;
         br.split_stride[b] = b < n_branches ? split_stride[b] : 0;
     }

@@ -68,3 +68,68 @@ class PreNormBlock(Part):
             if not part.handles_pending:
                 ctx.settle(h)
             part.forward(ctx, x, h)
+
+
+@register_part("block", "sandwich")
+class SandwichBlock(Part):
+    """Norms before and after every sublayer: x += s * post_norm1(mixer(norm1(x))), then
+    x += s * post_norm2(ffn(norm2(x))), s one number of the layer. The sublayers hand their output over as
+    float32 rows (or split sums) instead of adding it into the stream: the mixer by ``branch_output(ctx, x,
+    name)``, the feed-forward by ``output(ctx, x, name) -> (y, bias or None)``; the norm after them adds
+    (``add_normed``). A layer without a feed-forward has only the first sublayer."""
+
+    def __init__(self, layer_spec):
+        super().__init__({}, "")
+        from ..errors import ConfigError
+        if layer_spec.post_norm1 is None or (layer_spec.ffn is not None and layer_spec.post_norm2 is None):
+            raise ConfigError("block.arrangement", "the sandwich arrangement needs post_norm1 (and post_norm2 with a feed-forward)")
+        self.scale = float(layer_spec.residual_scale)
+        self.norm1 = build_part("norm", layer_spec.norm1)
+        self.mixer = build_part("mixer", layer_spec.mixer)
+        self.post1 = build_part("norm", layer_spec.post_norm1)
+        self.ffn = build_part("ffn", layer_spec.ffn) if layer_spec.ffn is not None else None
+        self.norm2 = build_part("norm", layer_spec.norm2) if self.ffn is not None else None
+        self.post2 = build_part("norm", layer_spec.post_norm2) if self.ffn is not None else None
+        if not hasattr(self.mixer, "branch_output"):
+            raise ConfigError("mixer.kind", f"the mixer {self.mixer.kind!r} does not hand its output over (branch_output)")
+        if self.ffn is not None and not hasattr(self.ffn, "output"):
+            raise ConfigError("ffn.kind", f"the feed-forward {self.ffn.kind!r} does not hand its output over (output)")
+        for n in (self.post1, self.post2):
+            if n is not None and not hasattr(n, "add_normed"):
+                raise ConfigError("norm.kind", f"the norm {n.kind!r} cannot stand behind a sublayer (add_normed)")
+
+    def parts(self):
+        return tuple(p for p in (self.norm1, self.mixer, self.post1, self.norm2, self.ffn, self.post2) if p is not None)
+
+    def tensor_specs(self):
+        out = {}
+        for p in self.parts():
+            out.update(p.tensor_specs())
+        return out
+
+    def load(self, tensors, device, dtype):
+        for p in self.parts():
+            p.load(tensors, device, dtype)
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts())
+
+    @property
+    def graph_safe_any_step(self):
+        return all(p.graph_safe_any_step for p in self.parts())
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def query_tile_sizes(self):
+        return self.mixer.query_tile_sizes()
+
+    def forward(self, ctx, h):
+        ctx.settle(h)                       # whatever a layer of another arrangement left undone
+        x = self.norm1.forward(ctx, h)
+        self.post1.add_normed(ctx, self.mixer.branch_output(ctx, x, "mixer_out"), h, self.scale)
+        if self.ffn is not None:
+            x = self.norm2.forward(ctx, h)
+            y, bias = self.ffn.output(ctx, x, "ffn_out")
+            self.post2.add_normed(ctx, y, h, self.scale, bias)

@@ -19,13 +19,14 @@ class TokenEmbedding(Part):
         super().__init__(params, prefix)
         self.vocab_size = int(params["vocab_size"])
         self.hidden_size = int(params["hidden_size"])
+        self.tensor = params.get("tensor") or self.prefix + "weight"      # the table's full name
         self.weight = None
 
     def tensor_specs(self):
-        return {self.prefix + "weight": TensorSpec((self.vocab_size, self.hidden_size), "embedding")}
+        return {self.tensor: TensorSpec((self.vocab_size, self.hidden_size), "embedding")}
 
     def load(self, tensors, device, dtype):
-        self.weight = to_device(tensors[self.prefix + "weight"], device, dtype)
+        self.weight = to_device(tensors[self.tensor], device, dtype)
 
     def forward(self, ctx, tokens, out, err):
         ops.embed_gather(self.weight, tokens, out, err)

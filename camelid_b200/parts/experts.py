@@ -1,0 +1,103 @@
+"""A routed feed-forward (mixture of experts): every row goes through the ``top`` of ``experts`` small
+gated feed-forwards that a linear router picks for it, and, where the layer has one, through a shared
+expert that every row uses.
+
+    z = x Wr^T (float32)            s = sigmoid(z)   or   softmax(z) over the experts   (``scoring``)
+    chosen: the ``top`` experts with the largest s;  weights w = s of the chosen (``renormalize``: / their sum)
+    expert_e(u) = Wd_e (silu(Wg_e u) * (Wu_e u))
+    y = sum over the chosen of expert_e(w x)          (``weight_on`` "input")
+      = sum over the chosen of w expert_e(x)          (``weight_on`` "output")
+    y += shared(x)
+
+Tensors under the prefix: ``router`` [experts, hidden]; per expert ``e<i>.gate``, ``e<i>.up`` [ff, hidden] and
+``e<i>.down`` [hidden, ff]; the shared expert's under ``shared.`` with the same three names. The experts'
+matrices are stacked into three tensors at load time. Router logits, scores and weights are float32; the
+row order of the grouped products is made on the device (``csrc/experts.cu``), so the part runs inside
+captured graphs.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.plan import PartSpec
+from ..csrc import ops
+from ..errors import ConfigError
+from . import linear
+from .base import Part, TensorSpec, build_part, register_part, to_device
+
+
+@register_part("ffn", "routed_experts")
+class RoutedExperts(Part):
+    graph_safe = True
+    graph_safe_any_step = True
+    handles_pending = True
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden_size = int(params["hidden_size"])
+        self.experts = int(params["experts"])
+        self.top = int(params["top"])
+        self.ff = int(params["expert_size"])
+        self.scoring = params.get("scoring") or "sigmoid"
+        self.renormalize = bool(params.get("renormalize", False))
+        self.weight_on = params.get("weight_on") or "output"
+        if not 1 <= self.top <= self.experts:
+            raise ConfigError("top", f"each row picks 1..{self.experts} experts, got {self.top}")
+        if self.experts > 1024:
+            raise ConfigError("experts", f"the routing kernel takes up to 1,024 experts, got {self.experts}")
+        if self.scoring not in ("sigmoid", "softmax"):
+            raise ConfigError("scoring", f"unknown scoring {self.scoring!r}; known: sigmoid, softmax")
+        if self.weight_on not in ("input", "output"):
+            raise ConfigError("weight_on", f"the weight multiplies the expert's 'input' or 'output', got {self.weight_on!r}")
+        self.shared = None
+        if params.get("shared_size"):
+            self.shared = build_part("ffn", PartSpec("swiglu", {"hidden_size": self.hidden_size,
+                                                                "intermediate_size": int(params["shared_size"]),
+                                                                "names": ("gate", "up", "down")}, prefix + "shared."))
+        self.w_router = self.w_gate = self.w_up = self.w_down = None
+
+    def tensor_specs(self):
+        p, hid = self.prefix, self.hidden_size
+        specs = {p + "router": TensorSpec((self.experts, hid))}
+        for e in range(self.experts):
+            specs[f"{p}e{e}.gate"] = TensorSpec((self.ff, hid))
+            specs[f"{p}e{e}.up"] = TensorSpec((self.ff, hid))
+            specs[f"{p}e{e}.down"] = TensorSpec((hid, self.ff))
+        if self.shared is not None:
+            specs.update(self.shared.tensor_specs())
+        return specs
+
+    def load(self, tensors, device, dtype):
+        p = self.prefix
+        self.w_router = to_device(tensors[p + "router"], device, dtype)
+        stack = lambda n: torch.stack([to_device(tensors[f"{p}e{e}.{n}"], device, dtype)       # noqa: E731
+                                       for e in range(self.experts)]).contiguous()
+        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        if self.shared is not None:
+            self.shared.load(tensors, device, dtype)
+
+    def output(self, ctx, x, name: str):
+        """(y, None): float32 [rows, hidden] in the step's buffer ``name``."""
+        rows, top, E = x.shape[0], self.top, self.experts
+        pairs = rows * top
+        i32 = lambda n, k: ctx.buffer(f"{name}_{n}", (k,), torch.int32)        # noqa: E731
+        logits = linear.product_rows_f32(ctx, x, self.w_router, name + "_router")
+        ids, wts = i32("ids", pairs), ctx.buffer(name + "_wts", (pairs,), torch.float32)
+        ops.route_topk(logits, top, self.scoring == "softmax", self.renormalize, ids, wts)
+        rank, counts, offsets, tile_first = i32("rank", pairs), i32("counts", E), i32("offsets", E + 1), i32("tiles", E + 1)
+        ops.expert_plan(ids, E, rank, counts, offsets, tile_first)
+        xs, place = ctx.buffer(name + "_xs", (pairs, self.hidden_size)), i32("place", pairs)
+        ops.expert_gather(x, ids, wts, rank, offsets, top, self.weight_on == "input", xs, place)
+        act = ctx.buffer(name + "_eact", (pairs, self.ff))
+        ops.expert_gemm(xs, self.w_gate, self.w_up, act, offsets, tile_first)
+        ys = ctx.buffer(name + "_ys", (pairs, self.hidden_size), torch.float32)
+        ops.expert_gemm(act, self.w_down, None, ys, offsets, tile_first)
+        shared = self.shared.output(ctx, x, name + "_shared")[0] if self.shared is not None else None
+        out = ctx.buffer(name, (rows, self.hidden_size), torch.float32)
+        ops.expert_combine(ys, place, wts, top, self.weight_on == "output", shared, out)
+        return out, None
+
+    def forward(self, ctx, x, residual):
+        y, _ = self.output(ctx, x, "experts_out")
+        ctx.settle(residual)
+        ops.add_partials(residual, y.unsqueeze(0))

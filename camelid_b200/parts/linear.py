@@ -176,15 +176,20 @@ def product_rows_f32(ctx, x: torch.Tensor, w: torch.Tensor, name: str) -> torch.
     return part[0]
 
 
-def product_act(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, name: str, gelu: bool) -> None:
-    """out = act(x @ w.T) in the compute type, act GELU (tanh form) or none. Few rows: split sums through
-    one kernel that adds them and applies the activation; many rows: the product's store, then the activation."""
+def product_act(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, name: str, gelu: bool = False, act: int | None = None,
+                bias=None) -> None:
+    """out = act(x @ w.T + bias) in the compute type; ``act`` one of ``ops.ACT_*`` (``gelu``: the tanh form of GELU),
+    ``bias`` float32 [out] or None. Few rows: split sums through one kernel that adds them and the bias and applies
+    the activation; many rows: the product's store, then bias and activation in place."""
+    code = act if act is not None else (ops.ACT_GELU_TANH if gelu else ops.ACT_NONE)
     part = partial_sums(ctx, x, w, name)
     if part is not None:
-        ops.act_from_partials(part, out, gelu)
+        ops.act_from_partials(part, out, act=code, bias=bias)
         return
     linear(ctx, x, w, out, STORE)
-    if gelu:
+    if bias is not None or code == ops.ACT_RELU_SQUARED:
+        ops.bias_act_(out, bias, code)
+    elif code == ops.ACT_GELU_TANH:
         ops.gelu_tanh_(out)
 
 

@@ -46,3 +46,8 @@ class RMSNorm(Part):
         pending, ctx.pending = ctx.pending, None            # split sums still to be added to h: added here
         ops.rmsnorm(h, self.weight, self.eps, out, rows_index, pending)
         return out
+
+    def add_normed(self, ctx, y, residual, scale: float = 1.0, bias=None) -> None:
+        """residual += scale * rmsnorm(y + bias) * w: this norm on a sublayer's output rows ``y`` (float32
+        [rows, hidden], or split sums [splits, rows, hidden] that are added first), added into the stream."""
+        ops.norm_combine([(y, self.weight)], residual, self.eps, scale, [bias])

@@ -1,5 +1,8 @@
 """Position encodings. The rotary one owns its per-pair frequencies; the mixer's kernel
-turns position * frequency into sine and cosine in float32 and rotates split-half pairs.
+turns position * frequency into sine and cosine in float32 and rotates pairs of channels:
+``pairing`` "split" pairs channel i with i + rotary_dim / 2 (the default), "interleaved" pairs
+channel 2i with 2i + 1 (the kernels of the windowed attention take both; the dense attention's
+kernels take "split").
 
 Frequencies as the reference computes them, in float32: f_i = theta^(-2i / rotary_dim)
 (src/inference/rope.rs:526-537), then for ``llama3`` scaling: wavelength = 2 pi / f; below
@@ -51,6 +54,9 @@ class RotaryEncoding(Part):
             raise ConfigError("rotary_dim", f"must be even, got {self.rotary_dim}")
         self.theta = float(params["theta"])
         self.scaling = params.get("scaling")
+        self.pairing = params.get("pairing") or "split"
+        if self.pairing not in ("split", "interleaved"):
+            raise ConfigError("pairing", f"unknown pairing {self.pairing!r}; known: split, interleaved")
         self.inv_freq = None
 
     def load(self, tensors, device, dtype):
@@ -66,6 +72,7 @@ class NoPositionEncoding(Part):
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.rotary_dim = 0
+        self.pairing = "split"
         self.inv_freq = None
 
     def load(self, tensors, device, dtype):

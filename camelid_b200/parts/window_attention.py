@@ -1,12 +1,23 @@
-"""Softmax attention over a sliding window without rotation, as a mixer: grouped queries, keys
-and values of different sizes, optional per-head RMS norm of q and k (one weight per channel,
-shared by the heads), an optional penalty on distance
+"""Softmax attention over a limited stretch of keys, as a mixer: grouped queries, keys and values of
+different sizes, and a set of options that designs combine:
 
-    score(i, j) = (q_i . k_j) * scale - r1[head] * ln(1 + r2[head] * (i - j)),    0 <= i - j < window,
+* ``window``: a query sees the last ``window`` keys; ``chunk``: it sees the keys of its own block of
+  ``chunk`` positions (blocks counted from position 0 of the sequence); neither: all keys before it.
+* ``qk_norm``: RMS norm of q and k, ``"head"`` (or True) per head with one weight per channel shared by
+  the heads, ``"full"`` over the whole projection (all heads at once) with a weight per column.
+* ``position``: a rotary encoding (``parts/position.py``) applied to q and k after the norm, pairs of
+  neighbouring channels or of the two halves; absent: no rotation.
+* ``distance_penalty`` ``"log"``:
 
-and an optional output gate: the concatenated heads times sigmoid(x Wg^T) before the output
-projection. Tensors under the prefix: ``q``, ``k``, ``v``, ``o`` (and ``g``, ``q.norm``,
-``k.norm``, ``r1``, ``r2`` where the options ask for them), linear weights [out, in].
+      score(i, j) = (q_i . k_j) * scale - r1[head] * ln(1 + r2[head] * (i - j)).
+
+* ``sink``: one learned number per head whose exponential is one more term of the softmax denominator
+  (no key, no value, not scaled).
+* ``output_gate``: the heads times sigmoid(x Wg^T) before the output projection, ``"channel"`` (or True)
+  a number per channel of every head, ``"head"`` one number per head.
+
+Tensors under the prefix: ``q``, ``k``, ``v``, ``o`` (and ``g``, ``q.norm``, ``k.norm``, ``r1``, ``r2``,
+``sink`` where the options ask for them), linear weights [out, in].
 
 Scores, softmax weights and the norms are float32; keys and values lie in the paged cache in
 the compute type, and a windowed group gives back the pages no later query can see.
@@ -16,10 +27,11 @@ from __future__ import annotations
 import torch
 
 from ..cache.book import KVSpec
+from ..config.plan import PartSpec
 from ..csrc import ops
 from ..errors import ConfigError
 from . import linear
-from .base import Part, TensorSpec, register_part, to_device
+from .base import Part, TensorSpec, build_part, register_part, to_device
 
 
 @register_part("mixer", "window_attention")
@@ -37,9 +49,20 @@ class WindowAttention(Part):
         self.value_dim = int(params.get("value_dim") or self.head_dim)
         self.window = int(params["window"]) if params.get("window") else None
         self.scale = float(params["scale"]) if params.get("scale") is not None else self.head_dim ** -0.5
-        self.qk_norm = bool(params.get("qk_norm", False))
+        self.qk_norm = {False: None, None: None, True: "head"}.get(params.get("qk_norm", False), params.get("qk_norm"))
         self.penalty = params.get("distance_penalty")
-        self.output_gate = bool(params.get("output_gate", False))
+        self.output_gate = {False: None, None: None, True: "channel"}.get(params.get("output_gate", False), params.get("output_gate"))
+        self.chunk = int(params["chunk"]) if params.get("chunk") else None
+        self.sink = bool(params.get("sink", False))
+        self.position = build_part("position", params.get("position") or PartSpec("none"))
+        if self.qk_norm not in (None, "head", "full"):
+            raise ConfigError("qk_norm", f"unknown q/k norm {self.qk_norm!r}; known: head, full")
+        if self.output_gate not in (None, "channel", "head"):
+            raise ConfigError("output_gate", f"unknown output gate {self.output_gate!r}; known: channel, head")
+        if self.chunk is not None and self.chunk <= 0:
+            raise ConfigError("chunk", f"must be greater than zero, got {self.chunk}")
+        if self.position.rotary_dim > self.head_dim:
+            raise ConfigError("rotary_dim", f"{self.position.rotary_dim} exceeds the head size {self.head_dim}")
         if self.num_kv_heads <= 0 or self.num_heads % self.num_kv_heads:
             raise ConfigError("num_kv_heads", f"{self.num_kv_heads} kv heads do not divide {self.num_heads} heads")
         if self.penalty not in (None, "log"):
@@ -52,18 +75,24 @@ class WindowAttention(Part):
         self.k_width = self.num_kv_heads * self.head_dim
         self.v_width = self.num_kv_heads * self.value_dim
         self.o_width = self.num_heads * self.value_dim
+        self.gate_width = {None: 0, "channel": self.o_width, "head": self.num_heads}[self.output_gate]
+        # q and k that are rotated, or normed over all heads at once, go through the preparing kernel that does both
+        self.prepare = self.position.rotary_dim > 0 or self.qk_norm == "full"
         self.gate_col = self.q_width + self.k_width + self.v_width
-        self.w_in = self.w_o = self.q_w = self.k_w = self.r1 = self.r2 = None
+        self.w_in = self.w_o = self.q_w = self.k_w = self.r1 = self.r2 = self.sink_w = None
 
     def tensor_specs(self):
         p, hid = self.prefix, self.hidden_size
         specs = {p + "q": TensorSpec((self.q_width, hid)), p + "k": TensorSpec((self.k_width, hid)),
                  p + "v": TensorSpec((self.v_width, hid)), p + "o": TensorSpec((hid, self.o_width))}
         if self.output_gate:
-            specs[p + "g"] = TensorSpec((self.o_width, hid))
+            specs[p + "g"] = TensorSpec((self.gate_width, hid))
         if self.qk_norm:
-            specs[p + "q.norm"] = TensorSpec((self.head_dim,), "norm")
-            specs[p + "k.norm"] = TensorSpec((self.head_dim,), "norm")
+            full = self.qk_norm == "full"
+            specs[p + "q.norm"] = TensorSpec((self.q_width if full else self.head_dim,), "norm")
+            specs[p + "k.norm"] = TensorSpec((self.k_width if full else self.head_dim,), "norm")
+        if self.sink:
+            specs[p + "sink"] = TensorSpec((self.num_heads,), "input_bias")
         if self.penalty:
             specs[p + "r1"] = TensorSpec((self.num_heads,), "fraction")
             specs[p + "r2"] = TensorSpec((self.num_heads,), "fraction")
@@ -79,13 +108,22 @@ class WindowAttention(Part):
             self.q_w, self.k_w = f32("q.norm"), f32("k.norm")
         if self.penalty:
             self.r1, self.r2 = f32("r1"), f32("r2")
+        if self.sink:
+            self.sink_w = f32("sink")
+        self.position.load(tensors, device, dtype)
 
     def cache_spec(self):
         return KVSpec(self.num_kv_heads, self.head_dim, self.window,
-                      self.value_dim if self.value_dim != self.head_dim else None)
+                      self.value_dim if self.value_dim != self.head_dim else None, self.chunk)
+
+    @property
+    def _tc_prompts(self) -> bool:
+        """Whether prompts can run on the tcgen05 kernel of the library's attention (bfloat16 and the sizes permitting)."""
+        return (self.value_dim == self.head_dim and self.head_dim in (64, 128) and self.chunk is None and not self.sink
+                and self.output_gate != "head")
 
     def query_tile_sizes(self):
-        if self.value_dim == self.head_dim and self.head_dim in (64, 128):
+        if self._tc_prompts:
             return [ops.attn_tc_tiling(self.num_heads, self.num_kv_heads)[0]]
         return []
 
@@ -98,12 +136,18 @@ class WindowAttention(Part):
         if proj is None:
             proj = linear.product_rows_f32(ctx, x, self.w_in, "wa_proj")
         q = ctx.buffer("wa_q", (n, self.q_width))
-        ops.qk_norm_kv_write(proj, self.q_w, self.k_w, self.eps, ctx.row_seq, ctx.row_pos, table, q, k_pages, v_pages,
-                             self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim)
+        if self.prepare:
+            pos = self.position
+            ops.qkv_prepare(proj, self.q_w, self.k_w, {None: 0, "head": 1, "full": 2}[self.qk_norm], self.eps, pos.inv_freq,
+                            pos.rotary_dim, pos.pairing == "interleaved", ctx.row_seq, ctx.row_pos, table, q, k_pages, v_pages,
+                            self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim)
+        else:
+            ops.qk_norm_kv_write(proj, self.q_w, self.k_w, self.eps, ctx.row_seq, ctx.row_pos, table, q, k_pages, v_pages,
+                                 self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim)
         out = ctx.buffer("wa_out", (n, self.o_width))
         # prompts in bfloat16 with keys and values of 64 or 128 channels: the tcgen05 kernel of the library's
         # attention (scores and softmax in float there too), then the gate; everything else on the kernel below
-        if not ctx.decode and self.value_dim == self.head_dim and ops.attn_tc_usable(q, out, self.head_dim):
+        if not ctx.decode and self._tc_prompts and ops.attn_tc_usable(q, out, self.head_dim):
             rows, hpc, chunks = ops.attn_tc_tiling(self.num_heads, self.num_kv_heads)
             tile_seq, tile_q0, n_tiles = ctx.query_tiles(rows)
             ops.attn_prefill_tc(q, out, k_pages, v_pages, table, tile_seq, tile_q0, n_tiles, ctx.seq_row0, ctx.seq_start,
@@ -114,7 +158,8 @@ class WindowAttention(Part):
             return out
         ops.window_attention(q, k_pages, v_pages, table, ctx.row_seq, ctx.row_pos, self.r1, self.r2,
                              proj if self.output_gate else None, self.gate_col, out, self.num_heads, self.num_kv_heads,
-                             self.head_dim, self.value_dim, self.window or 0, self.scale)
+                             self.head_dim, self.value_dim, self.window or 0, self.scale, self.chunk or 0, self.sink_w,
+                             self.output_gate == "head")
         return out
 
     def forward(self, ctx, x, residual):
