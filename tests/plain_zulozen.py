@@ -51,26 +51,42 @@ def sink_softmax(scores, mask, sink):
     return e / (e.sum(axis=-1, keepdims=True) + np.exp(sink - top))
 
 
-def attention(h, t, cfg, eps):
-    """h [tokens, width] (the normed rows); t: the mixer's tensors by short name; cfg: the mixer's sizes."""
-    H, G, D, Dv = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"]
+def project_qkv(h, t, cfg, eps, positions=None):
+    """q [n, H, D], k [n, G, D], v [n, G, Dv] of the normed rows h: q and k normed over all their columns, then rotated."""
+    H, G, D, Dv = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg.get("vdim", cfg["dim"])
     n = h.shape[0]
     q = rms_norm(h @ t["q"].T, t["q.norm"], eps).reshape(n, H, D)
     k = rms_norm(h @ t["k"].T, t["k.norm"], eps).reshape(n, G, D)
     v = (h @ t["v"].T).reshape(n, G, Dv)
-    pos = np.arange(n)
+    pos = np.arange(n) if positions is None else positions
     rot = cfg.get("rot")
     if rot and rot["dims"]:
         q = rotate_interleaved(q, pos, rot["dims"], rot["base"])
         k = rotate_interleaved(k, pos, rot["dims"], rot["base"])
-    mask = block_mask(n, (cfg.get("mask") or {}).get("size"))
-    gate = 1.0 / (1.0 + np.exp(-(h @ t["g"].T)))                    # [tokens, heads]
-    out = np.zeros((n, H, Dv))
+    return q, k, v
+
+
+def attend(q, k, v, scale, block, sink, gate=None):
+    """[n, H, Dv]: every head's weighted values; gate [n, H] (already a sigmoid) scales them."""
+    n, H, _ = q.shape
+    G = k.shape[1]
+    mask = block_mask(n, block)
+    out = np.zeros((n, H, v.shape[2]))
     for hd in range(H):
         g = hd // (H // G)
-        w = sink_softmax((q[:, hd] @ k[:, g].T) * cfg["scale"], mask, float(t["sink"][hd]))
-        out[:, hd] = (w @ v[:, g]) * gate[:, hd:hd + 1]
-    return out.reshape(n, H * Dv) @ t["o"].T
+        w = sink_softmax((q[:, hd] @ k[:, g].T) * scale, mask, float(sink[hd]) if sink is not None else -np.inf)
+        out[:, hd] = w @ v[:, g]
+        if gate is not None:
+            out[:, hd] *= gate[:, hd:hd + 1]
+    return out
+
+
+def attention(h, t, cfg, eps):
+    """h [tokens, width] (the normed rows); t: the mixer's tensors by short name; cfg: the mixer's sizes."""
+    q, k, v = project_qkv(h, t, cfg, eps)
+    gate = 1.0 / (1.0 + np.exp(-(h @ t["g"].T)))                    # [tokens, heads]
+    out = attend(q, k, v, cfg["scale"], (cfg.get("mask") or {}).get("size"), t["sink"], gate)
+    return out.reshape(h.shape[0], -1) @ t["o"].T
 
 
 def dense_ff(h, t):
@@ -83,10 +99,15 @@ def gated_expert(h, t, name):
     return ((g / (1.0 + np.exp(-g))) * (h @ t[name + ".up"].T)) @ t[name + ".down"].T
 
 
-def routed_ff(h, t, cfg):
+def routed_ff(h, t, cfg, margins=None):
+    """`margins` (a list) receives per row the gap between the last chosen router logit and the best one left out."""
     E, top = cfg["router"]["experts"], cfg["router"]["top"]
-    score = 1.0 / (1.0 + np.exp(-(h @ t["router"].T)))               # [tokens, experts]
+    logits = h @ t["router"].T
+    score = 1.0 / (1.0 + np.exp(-logits))                            # [tokens, experts]
     out = np.zeros_like(h)
+    if margins is not None:
+        ordered = -np.sort(-logits, axis=1)
+        margins.append(ordered[:, top - 1] - ordered[:, top] if top < E else np.full(h.shape[0], np.inf))
     for r in range(h.shape[0]):
         for e in np.argsort(-score[r], kind="stable")[:top]:
             out[r] += gated_expert(score[r, e] * h[r:r + 1], t, f"e{e}")[0]
@@ -99,8 +120,9 @@ def sub(tensors, prefix):
     return {k[len(prefix):]: np.asarray(v, dtype=np.float64) for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(config, tensors, tokens, probe=None):
-    """Logits [tokens, vocab] of one sequence; `probe(i, x)` sees the stream after every layer."""
+def forward(config, tensors, tokens, probe=None, margins=None):
+    """Logits [tokens, vocab] of one sequence; `probe(i, x)` sees the stream after every layer; `margins`
+    (a list) collects every routed layer's per-row margins of the choice."""
     eps, m = config["norm"]["eps"], config["residual_mult"]
     x = np.asarray(tensors["embed"], dtype=np.float64)[np.asarray(tokens)]
     for i, L in enumerate(config["layers"]):
@@ -111,7 +133,7 @@ def forward(config, tensors, tokens, probe=None):
         if L.get("mlp") is not None:
             t = sub(tensors, p + "mlp.")
             hn = rms_norm(x, tensors[p + "norm2"], eps)
-            y = dense_ff(hn, t) if L["mlp"]["kind"] == "dense" else routed_ff(hn, t, L["mlp"])
+            y = dense_ff(hn, t) if L["mlp"]["kind"] == "dense" else routed_ff(hn, t, L["mlp"], margins)
             x = x + m * rms_norm(y, tensors[p + "norm2b"], eps)
         if probe is not None:
             probe(i, x)
