@@ -6,7 +6,8 @@
 //
 //   route_topk      logits [rows, E] -> ids, weights [rows, top]   (sigmoid of the logit, or softmax over E)
 //   expert_rank     for expert e (one block each): the rank of each of its pairs among them, and their count
-//   expert_offsets  exclusive sums of the counts and of the counts' tiles of TM rows
+//   expert_offsets  exclusive sums of the counts and of the counts' tiles of `tile_rows` rows (64 for the product
+//                   below, 128 for the grouped product on the tensor cores)
 //   expert_gather   xs[offset[e] + rank] = x[row] (* weight): the experts' inputs, ordered by expert
 //   expert_gemm     C[pos] = xs[pos] W_e^T per stretch; plain float store, or silu(gate) * up in the compute type
 //   expert_combine  out[row] = shared[row] + sum over the row's choices of y[pos] (* weight)
@@ -96,16 +97,16 @@ __global__ void __launch_bounds__(256) expert_rank_kernel(const int* __restrict_
     if (threadIdx.x == 0) counts[e] = running;
 }
 
-// offsets[e] = pairs of experts before e; tile_first[e] = tiles of TM rows of experts before e (both E + 1 long).
+// offsets[e] = pairs of experts before e; tile_first[e] = tiles of tile_rows rows of experts before e (both E + 1 long).
 __global__ void __launch_bounds__(1024) expert_offsets_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets,
-                                                              int* __restrict__ tile_first) {
+                                                              int* __restrict__ tile_first, int tile_rows) {
     __shared__ int s_cnt[1024], s_tile[1024];
     pdl_wait();
     pdl_launch_dependents();
     const int t = threadIdx.x;
     const int c = t < E ? counts[t] : 0;
     s_cnt[t] = c;
-    s_tile[t] = (c + EX_TM - 1) / EX_TM;
+    s_tile[t] = (c + tile_rows - 1) / tile_rows;
     __syncthreads();
     for (int d = 1; d < 1024; d <<= 1) {                        // inclusive sums, doubling
         const int a = t >= d ? s_cnt[t - d] : 0, b = t >= d ? s_tile[t - d] : 0;
@@ -122,12 +123,12 @@ __global__ void __launch_bounds__(1024) expert_offsets_kernel(const int* __restr
 }
 
 extern "C" int cml_expert_plan(const int* ids, int pairs, int E, int* rank, int* counts, int* offsets, int* tile_first,
-                               void* stream) {
+                               int tile_rows, void* stream) {
     if (pairs <= 0) return 0;
-    if (E < 1 || E > 1024) return CML_ERR_BAD_SIZE;
+    if (E < 1 || E > 1024 || tile_rows < 1) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     launch_pdl(expert_rank_kernel, dim3(E), dim3(256), 0, s, ids, pairs, rank, counts);
-    launch_pdl(expert_offsets_kernel, dim3(1), dim3(1024), 0, s, (const int*)counts, E, offsets, tile_first);
+    launch_pdl(expert_offsets_kernel, dim3(1), dim3(1024), 0, s, (const int*)counts, E, offsets, tile_first, tile_rows);
     return cml_launch_status();
 }
 

@@ -59,6 +59,14 @@ struct TcParams {
     float in_inv_hidden, in_eps;
     int staged_ok;      // the outputs are aligned for 16-byte (float) and 8-byte (bfloat16) row pieces
     long split_stride;  // TC_STORE_F32 of a product split over K: split s writes C + s * split_stride (elements)
+    // Grouped product (one-block kernel, normal epilogues): the rows of A lie in stretches, one per group (the
+    // rows an expert of a routed feed-forward has to work on), and group g multiplies its stretch with its own
+    // matrix, rows g * rowsB .. (g + 1) * rowsB of B. grp_offsets[g] is the first row of stretch g (groups + 1
+    // entries), grp_tile_first[g] the number of 128-row tiles of the stretches before it; both are written on
+    // the device by an earlier kernel, and tiles_a is only an upper bound of the tiles there are.
+    const int* grp_offsets;
+    const int* grp_tile_first;
+    int groups;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -179,9 +187,9 @@ __device__ __forceinline__ float tc_row_scale(const float* __restrict__ sumsq, i
 // One 16-column chunk of one accumulator row, already in registers, to its place in the output.
 template <int EPI>
 __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const uint32_t (&r)[16], const uint32_t (&u)[16],
-                                                  int rowA, int colB, int split, int lane, int a_group0) {
+                                                  int rowA, int colB, int split, int lane, int a_group0, int row_limit) {
     if (EPI == TC_STORE || EPI == TC_STORE_F32 || EPI == TC_ADD_F32) {
-        if (rowA >= p.rowsA || colB >= p.rowsB) return;
+        if (rowA >= row_limit || colB >= p.rowsB) return;
         const int n_ok = min(16, p.rowsB - colB);
         if (EPI == TC_STORE) {
             bf16* dst = (bf16*)p.C + (size_t)rowA * p.ldc + colB;
@@ -221,7 +229,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const uint3
         // r: 16 gate columns, u: the 16 up columns of the same outputs
         const int out_col = colB / 2;
         const int inter = p.rowsB / 2;
-        if (rowA >= p.rowsA || out_col >= inter) return;
+        if (rowA >= row_limit || out_col >= inter) return;
         bf16* dst = (bf16*)p.C + (size_t)rowA * p.ldc + out_col;
         const int n_ok = min(16, inter - out_col);
         float a[16];
@@ -317,7 +325,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
 
-    auto item = [&](int w, int& a0, int& b0, int& split, int& kb_begin, int& n_kb) {
+    // b_row: the row of B the tile's loads start at (b0, or b0 within the group's own matrix); row_limit: the
+    // first row of A that is not the item's to write
+    auto item = [&](int w, int& a0, int& b0, int& split, int& kb_begin, int& n_kb, int& b_row, int& row_limit) {
         const int ta = w % p.tiles_a;
         const int rest = w / p.tiles_a;
         const int tb = rest % p.tiles_b;
@@ -326,15 +336,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         b0 = tb * BN;
         kb_begin = split * p.kb_per_split;
         n_kb = max(0, min(p.num_kb, kb_begin + p.kb_per_split) - kb_begin);
+        b_row = b0;
+        row_limit = p.rowsA;
+        if (p.grp_offsets != nullptr) {
+            if (ta >= p.grp_tile_first[p.groups]) {            // beyond the tiles there are: nothing to do or write
+                n_kb = 0;
+                row_limit = 0;
+                return;
+            }
+            int lo = 0, hi = p.groups;                         // the group whose tiles hold this one
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (p.grp_tile_first[mid] <= ta) lo = mid; else hi = mid;
+            }
+            a0 = p.grp_offsets[lo] + (ta - p.grp_tile_first[lo]) * TC_BM;
+            row_limit = p.grp_offsets[lo + 1];
+            b_row = lo * p.rowsB + b0;
+        }
     };
+    const bool grouped = p.grp_offsets != nullptr;
 
     if (warp == 0) {
         if (lane == 0) {
             int g = 0;                      // k-blocks issued so far by this block, over all its items
             bool waited = false, ok = true;
+            if (grouped) pdl_wait();        // the stretches themselves come from the kernel before
             for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-                int a0, b0, split, kb_begin, n_kb;
-                item(w, a0, b0, split, kb_begin, n_kb);
+                int a0, b0, split, kb_begin, n_kb, b_row, row_limit;
+                item(w, a0, b0, split, kb_begin, n_kb, b_row, row_limit);
+                b0 = b_row;
                 int i = 0;
                 if (!waited) {
                     // The weights do not depend on the kernel before: their first tiles are on
@@ -380,9 +410,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                                        ((uint32_t)(TC_BM >> 4) << 24);
             int g = 0, j = 0;                             // j counts the items that have k-blocks
             bool ok = true;
+            if (grouped) pdl_wait();
             for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-                int a0, b0, split, kb_begin, n_kb;
-                item(w, a0, b0, split, kb_begin, n_kb);
+                int a0, b0, split, kb_begin, n_kb, b_row, row_limit;
+                item(w, a0, b0, split, kb_begin, n_kb, b_row, row_limit);
                 if (n_kb == 0) continue;                  // the epilogue writes zeros on its own
                 const int buf = j & 1;
                 // the epilogue must have drained this accumulator (two items ago)
@@ -413,8 +444,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         bool ok = true;
         int j = 0;                               // counts the items that have k-blocks, as the MMA thread does
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-            int a0, b0, split, kb_begin, n_kb;
-            item(w, a0, b0, split, kb_begin, n_kb);
+            int a0, b0, split, kb_begin, n_kb, b_row, row_limit;
+            item(w, a0, b0, split, kb_begin, n_kb, b_row, row_limit);
             const int buf = j & 1;
             const int rowA = a0 + q * 32 + lane;
             if (n_kb > 0) {
@@ -434,7 +465,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 #pragma unroll
                     for (int i = 0; i < 16; ++i) r[i] = 0u, u[i] = 0u;
                 }
-                tc_epilogue_chunk<EPI>(p, r, u, rowA, b0 + c, split, lane, a0 + q * 32);
+                tc_epilogue_chunk<EPI>(p, r, u, rowA, b0 + c, split, lane, a0 + q * 32, row_limit);
             }
             if (n_kb > 0) {
                 tc_fence_before();
@@ -822,13 +853,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     }
                     __syncwarp();
                 } else if (EPI == TC_SWIGLU) {
-                    tc_epilogue_chunk<EPI>(p, r, u, rowA, b0 + c, 0, lane, 0);
+                    tc_epilogue_chunk<EPI>(p, r, u, rowA, b0 + c, 0, lane, 0, p.rowsA);
                 } else if (EPI == TC_ADD_NORM) {
                     ssq_out += tc_add_norm_chunk(p, r, rowA, b0 + c);
                     ssq_out += tc_add_norm_chunk(p, u, rowA, b0 + c + 16);
                 } else {
-                    tc_epilogue_chunk<EPI>(p, r, r, rowA, b0 + c, split, lane, 0);
-                    tc_epilogue_chunk<EPI>(p, u, u, rowA, b0 + c + 16, split, lane, 0);
+                    tc_epilogue_chunk<EPI>(p, r, r, rowA, b0 + c, split, lane, 0, p.rowsA);
+                    tc_epilogue_chunk<EPI>(p, u, u, rowA, b0 + c + 16, split, lane, 0, p.rowsA);
                 }
             }
             if (EPI == TC_ADD_NORM) {
@@ -931,6 +962,7 @@ extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, lo
     p.norm_w = nullptr; p.norm_w_dtype = 0; p.x_out = nullptr; p.ldx = 0; p.out_sumsq = nullptr;
     p.in_sumsq = nullptr; p.in_parts = 0; p.in_inv_hidden = 0.f; p.in_eps = 0.f; p.staged_ok = 0;
     p.split_stride = 0;
+    p.grp_offsets = nullptr; p.grp_tile_first = nullptr; p.groups = 0;
     p.independent = (epilogue == TC_T_PARTIAL || epilogue == TC_T_SWIGLU) ? 0 : 1;
     p.tiles_a = (rowsA + TC_BM - 1) / TC_BM;
     p.tiles_b = (rowsB + bn - 1) / bn;
@@ -954,6 +986,45 @@ extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, lo
     TC_CASE(128, TC_T_PARTIAL);
     TC_CASE(16, TC_T_SWIGLU); TC_CASE(32, TC_T_SWIGLU); TC_CASE(64, TC_T_SWIGLU);
     TC_CASE(128, TC_T_SWIGLU);
+#undef TC_CASE
+    return CML_ERR_BAD_SIZE;
+}
+
+// The grouped product: A [rowsA, K] in stretches (offsets, tile_first: see TcParams), B [groups * rowsB, K], group
+// g's matrix at rows g * rowsB. C[row] = A[row] B_g^T for the rows of stretch g: TC_STORE_F32 (float), TC_STORE
+// (bfloat16) or TC_SWIGLU (B_g packed gate/up rows in groups of 16; C [rowsA, rowsB / 2] bfloat16). bn 128 or 256.
+extern "C" int cml_gemm_tc_grouped(const void* A, long lda, int rowsA, const void* B, long ldb, int groups, int rowsB, int K,
+                                   void* C, long ldc, int epilogue, int bn, const int* offsets, const int* tile_first,
+                                   int* err, void* stream) {
+    if (rowsA <= 0 || rowsB <= 0 || groups <= 0) return 0;
+    if (K <= 0 || (K & 7)) return CML_ERR_BAD_SIZE;
+    if (epilogue != TC_STORE && epilogue != TC_STORE_F32 && epilogue != TC_SWIGLU) return CML_ERR_BAD_SIZE;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, rowsA, K, lda, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mb, B, (long)groups * rowsB, K, ldb, bn);
+    if (rc) return rc;
+    TcParams p;
+    p.C = C; p.ldc = ldc; p.rowsA = rowsA; p.rowsB = rowsB;
+    p.num_kb = (K + TC_BK - 1) / TC_BK;
+    p.kb_per_split = p.num_kb;
+    p.err = err;
+    p.norm_w = nullptr; p.norm_w_dtype = 0; p.x_out = nullptr; p.ldx = 0; p.out_sumsq = nullptr;
+    p.in_sumsq = nullptr; p.in_parts = 0; p.in_inv_hidden = 0.f; p.in_eps = 0.f; p.staged_ok = 0;
+    p.split_stride = 0;
+    p.grp_offsets = offsets; p.grp_tile_first = tile_first; p.groups = groups;
+    p.independent = 1;
+    p.tiles_a = (rowsA + TC_BM - 1) / TC_BM + (groups < rowsA ? groups : rowsA);      // at most this many tiles
+    p.tiles_b = (rowsB + bn - 1) / bn;
+    p.splits = 1;
+    const long work = (long)p.tiles_a * p.tiles_b;
+    if (work > 0x7fffffffL) return CML_ERR_BAD_SIZE;
+    const int sms = cml_sm_count();
+    dim3 grid((unsigned)(work < sms ? work : sms), 1, 1);
+    cudaStream_t s = (cudaStream_t)stream;
+#define TC_CASE(BN_, EPI_) if (bn == BN_ && epilogue == EPI_) return launch_tc<BN_, EPI_>(ma, mb, p, grid, s)
+    TC_CASE(128, TC_STORE); TC_CASE(128, TC_STORE_F32); TC_CASE(128, TC_SWIGLU);
+    TC_CASE(256, TC_STORE); TC_CASE(256, TC_STORE_F32); TC_CASE(256, TC_SWIGLU);
 #undef TC_CASE
     return CML_ERR_BAD_SIZE;
 }
@@ -1016,6 +1087,7 @@ static int gemm_tc_pair_launch(const void* A, long lda, int rowsA, const void* B
     p.tiles_b = (rowsB + bn - 1) / bn;
     p.splits = splits;
     p.split_stride = nm.split_stride;
+    p.grp_offsets = nullptr; p.grp_tile_first = nullptr; p.groups = 0;
     p.norm_w = nm.norm_w; p.norm_w_dtype = nm.norm_w_dtype; p.x_out = (bf16*)nm.x_out; p.ldx = nm.ldx;
     p.out_sumsq = nm.out_sumsq;
     p.in_sumsq = nm.in_sumsq; p.in_parts = nm.in_parts;

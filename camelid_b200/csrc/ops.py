@@ -117,7 +117,9 @@ _SIGNATURES = {
                                               c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                               c_int, c_int, c_int, c_int, c_void_p],
     ("experts", "cml_route_topk"): [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
-    ("experts", "cml_expert_plan"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    ("experts", "cml_expert_plan"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    ("gemm_tc", "cml_gemm_tc_grouped"): [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_long, c_int,
+                                         c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("experts", "cml_expert_gather"): [c_void_p, c_int, c_long, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                        c_int, c_void_p, c_void_p, c_void_p],
     ("experts", "cml_expert_gemm"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
@@ -644,14 +646,18 @@ def route_topk(logits: torch.Tensor, top: int, softmax: bool, renorm: bool, ids:
                                             1 if renorm else 0, _p(ids), _p(wts), _stream()), "route_topk")
 
 
-def expert_plan(ids: torch.Tensor, experts: int, rank, counts, offsets, tile_first):
+EXPERT_TILE_ROWS, EXPERT_TILE_ROWS_TC = 64, 128      # rows of a tile of the grouped products: CUDA cores, tensor cores
+
+
+def expert_plan(ids: torch.Tensor, experts: int, rank, counts, offsets, tile_first, tile_rows: int = EXPERT_TILE_ROWS):
     """Orders the (row, choice) pairs by expert: ``rank`` of each pair among its expert's, ``counts`` per expert,
-    ``offsets`` [experts + 1] and the first tile of every expert's stretch ``tile_first`` [experts + 1]."""
+    ``offsets`` [experts + 1] and the first tile (of ``tile_rows`` rows) of every expert's stretch ``tile_first``
+    [experts + 1]."""
     _dev(ids, rank, counts, offsets, tile_first)
     assert all(t.dtype == torch.int32 and t.is_contiguous() for t in (ids, rank, counts, offsets, tile_first))
     assert rank.numel() == ids.numel() and counts.numel() >= experts and offsets.numel() > experts and tile_first.numel() > experts
     _check(_fn("experts", "cml_expert_plan")(_p(ids), ids.numel(), experts, _p(rank), _p(counts), _p(offsets), _p(tile_first),
-                                             _stream()), "expert_plan", launches=2)
+                                             int(tile_rows), _stream()), "expert_plan", launches=2)
 
 
 def expert_gather(x: torch.Tensor, ids, wts, rank, offsets, top: int, scale_input: bool, xs: torch.Tensor, pos_of_pair):
@@ -675,6 +681,22 @@ def expert_gemm(a: torch.Tensor, w: torch.Tensor, w2, out: torch.Tensor, offsets
     assert w2 is None or (w2.shape == w.shape and w2.is_contiguous() and w2.dtype == w.dtype)
     _check(_fn("experts", "cml_expert_gemm")(_p(a), _p(w), _p(w2), dtype_code(a.dtype), _p(out), pairs, n, k, experts,
                                              _p(offsets), _p(tile_first), _stream()), "expert_gemm")
+
+
+def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, offsets, tile_first, err: torch.Tensor):
+    """The grouped product on the tensor cores (bfloat16): per expert e, out[stretch e] = a[stretch e] @ w[e].T with
+    epilogue TC_STORE_F32 (float32 out), TC_STORE (bfloat16) or TC_SWIGLU (w[e] packed gate/up rows in groups of 16,
+    out [rows, n / 2] bfloat16). ``offsets``, ``tile_first``: from ``expert_plan`` with tiles of 128 rows."""
+    _dev(a, w, out, offsets, tile_first, err)
+    rows, k = a.shape
+    experts, n, k2 = w.shape
+    assert k == k2 and a.dtype == w.dtype == torch.bfloat16 and w.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1
+    assert epilogue in (TC_STORE, TC_STORE_F32, TC_SWIGLU)
+    assert out.shape == (rows, n // 2 if epilogue == TC_SWIGLU else n)
+    assert out.dtype == (torch.float32 if epilogue == TC_STORE_F32 else torch.bfloat16)
+    bn = 256 if n % 256 == 0 and n >= 1024 else 128
+    _check(_fn("gemm_tc", "cml_gemm_tc_grouped")(_p(a), a.stride(0), rows, _p(w), k, experts, n, k, _p(out), out.stride(0),
+                                                 epilogue, bn, _p(offsets), _p(tile_first), _p(err), _stream()), "gemm_tc_grouped")
 
 
 def expert_combine(y: torch.Tensor, pos_of_pair, wts, top: int, scale_output: bool, shared, out: torch.Tensor):

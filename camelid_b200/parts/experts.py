@@ -73,6 +73,11 @@ class RoutedExperts(Part):
         stack = lambda n: torch.stack([to_device(tensors[f"{p}e{e}.{n}"], device, dtype)       # noqa: E731
                                        for e in range(self.experts)]).contiguous()
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        # bfloat16 with sizes the tensor-core kernel takes: gate and up packed per expert as the dense SwiGLU has them
+        self.w_gate_up = None
+        if dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and self.ff % 16 == 0 and str(device) != "cpu":
+            self.w_gate_up = torch.stack([linear.pack_gate_up(self.w_gate[e], self.w_up[e], 16) for e in range(self.experts)]).contiguous()
+            self.w_gate = self.w_up = None
         if self.shared is not None:
             self.shared.load(tensors, device, dtype)
 
@@ -85,13 +90,19 @@ class RoutedExperts(Part):
         ids, wts = i32("ids", pairs), ctx.buffer(name + "_wts", (pairs,), torch.float32)
         ops.route_topk(logits, top, self.scoring == "softmax", self.renormalize, ids, wts)
         rank, counts, offsets, tile_first = i32("rank", pairs), i32("counts", E), i32("offsets", E + 1), i32("tiles", E + 1)
-        ops.expert_plan(ids, E, rank, counts, offsets, tile_first)
+        tc = self.w_gate_up is not None
+        ops.expert_plan(ids, E, rank, counts, offsets, tile_first, ops.EXPERT_TILE_ROWS_TC if tc else ops.EXPERT_TILE_ROWS)
         xs, place = ctx.buffer(name + "_xs", (pairs, self.hidden_size)), i32("place", pairs)
         ops.expert_gather(x, ids, wts, rank, offsets, top, self.weight_on == "input", xs, place)
         act = ctx.buffer(name + "_eact", (pairs, self.ff))
-        ops.expert_gemm(xs, self.w_gate, self.w_up, act, offsets, tile_first)
         ys = ctx.buffer(name + "_ys", (pairs, self.hidden_size), torch.float32)
-        ops.expert_gemm(act, self.w_down, None, ys, offsets, tile_first)
+        if tc:          # the grouped products on the tensor cores; float32 and odd sizes on the CUDA cores
+            err = linear._err_word(x.device)
+            ops.gemm_tc_grouped(xs, self.w_gate_up, act, ops.TC_SWIGLU, offsets, tile_first, err)
+            ops.gemm_tc_grouped(act, self.w_down, ys, ops.TC_STORE_F32, offsets, tile_first, err)
+        else:
+            ops.expert_gemm(xs, self.w_gate, self.w_up, act, offsets, tile_first)
+            ops.expert_gemm(act, self.w_down, None, ys, offsets, tile_first)
         shared = self.shared.output(ctx, x, name + "_shared")[0] if self.shared is not None else None
         out = ctx.buffer(name, (rows, self.hidden_size), torch.float32)
         ops.expert_combine(ys, place, wts, top, self.weight_on == "output", shared, out)

@@ -311,7 +311,7 @@ def test_sink_alone_takes_its_share(cuda):
     assert torch.allclose(out.cpu(), torch.full((1, Dv), 2.0), atol=1e-6)
 
 
-@pytest.mark.parametrize("rows,E,top,ff", [(1, 5, 2, 24), (7, 3, 3, 16), (300, 5, 2, 40), (150, 16, 1, 8)])
+@pytest.mark.parametrize("rows,E,top,ff", [(1, 5, 2, 24), (7, 3, 3, 16), (300, 5, 2, 48), (150, 16, 1, 8), (700, 3, 2, 272)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_routed_experts_kernels(cuda, rows, E, top, ff, dtype):
     """Routing, ordering by expert, the grouped products and the sum against the plain routed feed-forward: experts with
@@ -360,6 +360,18 @@ def test_routed_experts_kernels(cuda, rows, E, top, ff, dtype):
     ops.expert_combine(ys, place, wts, top, False, None, out)
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     assert float((out.double().cpu() - ref).abs().max()) < tol * max(1.0, float(ref.abs().max()))
+    if dtype == torch.bfloat16 and ff % 16 == 0:
+        # the same through the grouped product on the tensor cores (stretches cut into tiles of 128 rows)
+        from camelid_b200.parts import linear
+        ops.expert_plan(ids, E, rank, counts, offsets, tiles, ops.EXPERT_TILE_ROWS_TC)
+        packed = torch.stack([linear.pack_gate_up(t[f"e{e}.gate"], t[f"e{e}.up"], 16) for e in range(E)]).to(cuda).contiguous()
+        err = torch.zeros(1, dtype=torch.int32, device=cuda)
+        act2, ys2 = torch.full_like(act, float("nan")), torch.full_like(ys, float("nan"))
+        ops.gemm_tc_grouped(xs, packed, act2, ops.TC_SWIGLU, offsets, tiles, err)
+        ops.gemm_tc_grouped(act2, stack("down"), ys2, ops.TC_STORE_F32, offsets, tiles, err)
+        ops.expert_combine(ys2, place, wts, top, False, None, out)
+        assert int(err.item()) == 0
+        assert float((out.double().cpu() - ref).abs().max()) < tol * max(1.0, float(ref.abs().max()))
 
 
 def test_dense_feed_forward_and_the_norm_behind_it(cuda):
