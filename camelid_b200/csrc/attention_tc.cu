@@ -35,6 +35,11 @@ struct AtParams {
     int n_tiles;
     const float* r1;        // per head, or null: the score loses r1 ln(1 + r2 (i - j)), a penalty on distance
     const float* r2;
+    int chunk;              // > 0: a query sees only the keys of its own block of `chunk` positions (counted from 0)
+    const float* sink;      // per head, or null: one more term exp(sink) in the softmax denominator (no key, no value)
+    const float* gate;      // float [rows, gate_ld], or null: head h of row r is scaled by sigmoid(gate[r, gate_col + h])
+    long gate_ld;
+    int gate_col;
 };
 
 __device__ __forceinline__ uint32_t at_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -207,7 +212,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
     const int hpc = p.heads_per_cta;
     const int rows_in_tile = min(p.rows_per_tile, n_new - q0);
     const int kend = start + q0 + rows_in_tile;
-    const int kbeg = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;
+    int kbeg = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;
+    if (ap.chunk > 0) kbeg = max(kbeg, (start + q0) - (start + q0) % ap.chunk);       // the first row's own block of positions
     const int t_first = kbeg / AT_KEYS;
     const int n_tiles_k = (kend + AT_KEYS - 1) / AT_KEYS - t_first;
 
@@ -316,7 +322,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
         const int hg = chunk * hpc + (i - r_local * hpc);
         const bool valid = (r_local < rows_in_tile) && (hg < group);
         const int pos = start + q0 + r_local;
-        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        if (ap.chunk > 0) lo = max(lo, pos - pos % ap.chunk);
         const size_t row = (size_t)(row0 + q0 + r_local);
         const int head = kvh * group + hg;
         {   // this row of Q into the swizzled tile
@@ -332,7 +339,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
             at_mbar_arrive(q_ready);
         }
         // smallest "lowest visible key" over the block's rows (first row), for the unmasked fast path
-        const int blk_lo = p.window > 0 ? max(0, start + q0 + rows_in_tile - 1 - p.window + 1) : 0;
+        int blk_lo = p.window > 0 ? max(0, start + q0 + rows_in_tile - 1 - p.window + 1) : 0;
+        if (ap.chunk > 0) {
+            const int last = start + q0 + rows_in_tile - 1;
+            blk_lo = max(blk_lo, last - last % ap.chunk);
+        }
         const float sl2 = p.scale * 1.4426950408889634f;       // scores are kept raw; exp2((s - m) * scale * log2 e)
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         // m is the reference the exponentials are taken against. It follows the running maximum
@@ -447,7 +458,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
             ok = at_mbar_wait(pv_full, (uint32_t)(n_tiles_k - 1) & 1u, abort_flag);
             if (ok) {
                 at_fence_after();
-                const float inv = valid ? 1.0f / l : 0.f;
+                if (ap.sink != nullptr && valid) {
+                    // the sink's term against the same reference as the keys' (raw scores times the scale; the sink is not scaled)
+                    const float m_ref = (m == -CUDART_INF_F) ? 0.f : m;
+                    l += at_exp2(fminf(fmaf(ap.sink[head], 1.4426950408889634f, -m_ref * sl2), 126.0f));
+                }
+                float inv = valid ? 1.0f / l : 0.f;
+                if (ap.gate != nullptr && valid) inv *= 1.0f / (1.0f + __expf(-ap.gate[row * ap.gate_ld + ap.gate_col + head]));
                 bf16* dst = (bf16*)p.out + row * p.out_stride + (size_t)head * HD;
 #pragma unroll
                 for (int c = 0; c < HD; c += 32) {
@@ -524,12 +541,16 @@ static int at_launch(const CUtensorMap& mk, const CUtensorMap& mv, AtParams ap, 
 // Tiles of rows_per_tile tokens with rows_per_tile * heads_per_cta <= 128; n_pages: pages of the pool.
 // q rows must be 16-byte aligned (q_stride and head_dim multiples of 8), the output likewise.
 // r1, r2 (float [n_heads] each, or both null): score(i, j) = (q . k) scale - r1[head] ln(1 + r2[head] (i - j)).
-extern "C" int cml_attn_prefill_tc_penalty(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                           const void* v_pages, long n_pages, const int* block_table, int max_blocks,
-                                           const int* tile_seq, const int* tile_q0, int n_tiles, const int* seq_row0,
-                                           const int* seq_start, const int* seq_new, int n_heads, int n_kv_heads,
-                                           int head_dim, int rows_per_tile, int heads_per_cta, int head_chunks, int window,
-                                           float scale, const float* r1, const float* r2, int* err, void* stream) {
+// chunk > 0: queries see only the keys of their own block of `chunk` positions; sink (float [n_heads] or null): one more
+// term exp(sink[head]) in the denominator; gate (float [rows, gate_ld] or null): head h of row r times
+// sigmoid(gate[r, gate_col + h]).
+extern "C" int cml_attn_prefill_tc_ext(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                       const void* v_pages, long n_pages, const int* block_table, int max_blocks,
+                                       const int* tile_seq, const int* tile_q0, int n_tiles, const int* seq_row0,
+                                       const int* seq_start, const int* seq_new, int n_heads, int n_kv_heads,
+                                       int head_dim, int rows_per_tile, int heads_per_cta, int head_chunks, int window,
+                                       float scale, const float* r1, const float* r2, int chunk, const float* sink,
+                                       const float* gate, long gate_ld, int gate_col, int* err, void* stream) {
     if (n_tiles <= 0) return 0;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return CML_ERR_BAD_SIZE;
     if (rows_per_tile < 1 || heads_per_cta < 1 || rows_per_tile * heads_per_cta > AT_ROWS) return CML_ERR_BAD_SIZE;
@@ -553,9 +574,21 @@ extern "C" int cml_attn_prefill_tc_penalty(const void* q, int q_stride, void* ou
     ap.err = err;
     ap.r1 = (r1 && r2) ? r1 : nullptr;
     ap.r2 = (r1 && r2) ? r2 : nullptr;
+    ap.chunk = chunk > 0 ? chunk : 0; ap.sink = sink; ap.gate = gate; ap.gate_ld = gate_ld; ap.gate_col = gate_col;
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 64) return at_launch<64>(mk, mv, ap, n_tiles, s);
     return at_launch<128>(mk, mv, ap, n_tiles, s);
+}
+
+extern "C" int cml_attn_prefill_tc_penalty(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                           const void* v_pages, long n_pages, const int* block_table, int max_blocks,
+                                           const int* tile_seq, const int* tile_q0, int n_tiles, const int* seq_row0,
+                                           const int* seq_start, const int* seq_new, int n_heads, int n_kv_heads,
+                                           int head_dim, int rows_per_tile, int heads_per_cta, int head_chunks, int window,
+                                           float scale, const float* r1, const float* r2, int* err, void* stream) {
+    return cml_attn_prefill_tc_ext(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, max_blocks, tile_seq,
+                                   tile_q0, n_tiles, seq_row0, seq_start, seq_new, n_heads, n_kv_heads, head_dim, rows_per_tile,
+                                   heads_per_cta, head_chunks, window, scale, r1, r2, 0, nullptr, nullptr, 0, 0, err, stream);
 }
 
 extern "C" int cml_attn_prefill_tc(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

@@ -54,6 +54,10 @@ _SIGNATURES = {
     ("attention_tc", "cml_attn_prefill_tc"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p,
                                               c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    ("attention_tc", "cml_attn_prefill_tc_ext"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p,
+                                                  c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+                                                  c_int, c_void_p, c_void_p, c_long, c_int, c_void_p, c_void_p],
     ("attention_tc", "cml_attn_prefill_tc_penalty"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p,
                                                       c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                       c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
@@ -983,19 +987,25 @@ def attn_tc_usable(q: torch.Tensor, out: torch.Tensor, head_dim: int) -> bool:
 
 def attn_prefill_tc(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_tiles, seq_row0, seq_start, seq_new,
                     n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, window, scale, err,
-                    r1=None, r2=None):
+                    r1=None, r2=None, chunk: int = 0, sink=None, head_gate=None, gate_col: int = 0):
     """bfloat16 prefill attention of packed query rows over the paged cache with tcgen05.mma. ``r1``, ``r2``
-    (float32 [heads]): the score of key j for query i loses r1 ln(1 + r2 (i - j))."""
-    _dev(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, seq_row0, seq_start, seq_new, err, r1, r2)
+    (float32 [heads]): the score of key j for query i loses r1 ln(1 + r2 (i - j)). ``chunk``: queries see only the
+    keys of their own block of ``chunk`` positions. ``sink`` (float32 [heads]): one more term exp(sink) in the
+    denominator. ``head_gate`` (float32 [rows, ...]): head h of row r times sigmoid(head_gate[r, gate_col + h])."""
+    _dev(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, seq_row0, seq_start, seq_new, err, r1, r2, sink, head_gate)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads and sink.is_contiguous())
+    assert head_gate is None or (head_gate.dtype == torch.float32 and head_gate.stride(1) == 1 and head_gate.shape[0] == q.shape[0]
+                                 and gate_col + n_heads <= head_gate.shape[1])
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == torch.bfloat16
     assert k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim) and k_pages.is_contiguous() and v_pages.is_contiguous()
     assert v_pages.shape == k_pages.shape
     if r1 is not None:
         assert r1.dtype == torch.float32 and r2.dtype == torch.float32 and r1.numel() == n_heads and r2.numel() == n_heads
-    _check(_fn("attention_tc", "cml_attn_prefill_tc_penalty")(
+    _check(_fn("attention_tc", "cml_attn_prefill_tc_ext")(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), k_pages.shape[0], _p(block_table),
         block_table.shape[1], _p(tile_seq), _p(tile_q0), n_tiles, _p(seq_row0), _p(seq_start), _p(seq_new), n_heads,
         n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, int(window or 0), float(scale), _p(r1), _p(r2),
+        int(chunk or 0), _p(sink), _p(head_gate), head_gate.stride(0) if head_gate is not None else 0, int(gate_col),
         _p(err), _stream()), "attn_prefill_tc")
 
 

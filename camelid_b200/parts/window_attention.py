@@ -119,8 +119,7 @@ class WindowAttention(Part):
     @property
     def _tc_prompts(self) -> bool:
         """Whether prompts can run on the tcgen05 kernel of the library's attention (bfloat16 and the sizes permitting)."""
-        return (self.value_dim == self.head_dim and self.head_dim in (64, 128) and self.chunk is None and not self.sink
-                and self.output_gate != "head")
+        return self.value_dim == self.head_dim and self.head_dim in (64, 128)
 
     def query_tile_sizes(self):
         if self._tc_prompts:
@@ -152,8 +151,9 @@ class WindowAttention(Part):
             tile_seq, tile_q0, n_tiles = ctx.query_tiles(rows)
             ops.attn_prefill_tc(q, out, k_pages, v_pages, table, tile_seq, tile_q0, n_tiles, ctx.seq_row0, ctx.seq_start,
                                 ctx.seq_new, self.num_heads, self.num_kv_heads, self.head_dim, rows, hpc, chunks,
-                                self.window or 0, self.scale, linear._err_word(q.device), self.r1, self.r2)
-            if self.output_gate:
+                                self.window or 0, self.scale, linear._err_word(q.device), self.r1, self.r2, self.chunk or 0,
+                                self.sink_w, proj if self.output_gate == "head" else None, self.gate_col)
+            if self.output_gate == "channel":
                 ops.gate_rows_(out, proj, self.gate_col)
             return out
         ops.window_attention(q, k_pages, v_pages, table, ctx.row_seq, ctx.row_pos, self.r1, self.r2,

@@ -297,6 +297,71 @@ def test_attention_kernels_at_a_blocks_edge_and_far_back(cuda, cut, block):
     assert float((got - ref).abs().max()) < 2e-5 * max(1.0, float(ref.abs().max()))
 
 
+@pytest.mark.parametrize("D,group,block", [(64, 3, 70), (128, 2, 200), (128, 1, 33), (64, 4, 1000)])
+def test_prompt_attention_on_tensor_cores_with_blocks_sink_and_gate(cuda, D, group, block):
+    """bfloat16 prompts with keys and values of 64 or 128 channels take the tcgen05 kernel: two sequences in one step, the
+    first a portion that starts at position 150 of its sequence (blocks are counted from position 0, not from the cut),
+    against the plain formula on the same bfloat16 q, k, v; a loved key just before a block's edge shows the edge."""
+    from camelid_b200.csrc import ops
+    from camelid_b200.parts import linear
+    gen = torch.Generator().manual_seed(7)
+    G, lens, starts = 2, [380, 67], [150, 0]
+    H = G * group
+    scale = D ** -0.5
+    tile_rows, hpc, chunks = ops.attn_tc_tiling(H, G)
+    sink = torch.randn(H, generator=gen) * 2
+    total = [s + n for s, n in zip(starts, lens)]
+    qs = [torch.randn(t, H, D, generator=gen).to(torch.bfloat16) for t in total]
+    ks = [torch.randn(t, G, D, generator=gen).to(torch.bfloat16) for t in total]
+    vs = [torch.randn(t, G, D, generator=gen).to(torch.bfloat16) for t in total]
+    edge = (total[0] // block) * block - 1 if block < total[0] else 5
+    ks[0][edge] = 0
+    ks[0][edge, :, 0] = 30.0
+    qs[0][:, :, 0] = 2.0
+    gates = [torch.randn(t, H, generator=gen) for t in total]
+    ref = torch.cat([torch.from_numpy(pz.attend(q.double().numpy(), k.double().numpy(), v.double().numpy(), scale, block,
+                                                sink.double().numpy(), 1 / (1 + np.exp(-g.double().numpy())))).reshape(t, H * D)[st:]
+                     for q, k, v, g, t, st in zip(qs, ks, vs, gates, total, starts)])
+    pages = [(t + 63) // 64 for t in total]
+    table = torch.full((2, max(pages)), -1, dtype=torch.int32)
+    table[0, :pages[0]] = torch.arange(pages[0]) + pages[1]
+    table[1, :pages[1]] = torch.arange(pages[1])
+    table = table.to(cuda)
+    kp = torch.zeros(sum(pages), G, 64, D, dtype=torch.bfloat16, device=cuda)
+    vp = torch.zeros_like(kp)
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device=cuda)      # noqa: E731
+    # the earlier part of the first sequence is in the cache already; then the step's rows
+    for seq_rows, st, n in ((0, 0, starts[0]), (None, None, None)):
+        if seq_rows == 0:
+            a = arrays(cuda, [0], [starts[0]])
+            a["row_seq"].zero_()
+            sl = [slice(0, starts[0]), None]
+            proj = torch.cat([qs[0][sl[0]].reshape(starts[0], -1), ks[0][sl[0]].reshape(starts[0], -1), vs[0][sl[0]].reshape(starts[0], -1)], 1)
+            ops.qk_norm_kv_write(proj.float().to(cuda), None, None, 1e-6, a["row_seq"], a["row_pos"], table,
+                                 torch.empty(starts[0], H * D, dtype=torch.bfloat16, device=cuda), kp, vp, H, G, D, D)
+    a = arrays(cuda, starts, lens)
+    rows = sum(lens)
+    cat = lambda xs: torch.cat([x[st:].reshape(t - st, -1) for x, t, st in zip(xs, total, starts)])      # noqa: E731
+    proj = torch.cat([cat(qs), cat(ks), cat(vs)], 1).float().to(cuda)
+    gate = cat(gates).to(cuda)
+    qn = torch.empty(rows, H * D, dtype=torch.bfloat16, device=cuda)
+    ops.qk_norm_kv_write(proj, None, None, 1e-6, a["row_seq"], a["row_pos"], table, qn, kp, vp, H, G, D, D)
+    tile_seq = [s for s, n in enumerate(lens) for _ in range(0, n, tile_rows)]
+    tile_q0 = [q0 for n in lens for q0 in range(0, n, tile_rows)]
+    row0 = [0, lens[0]]
+    out = torch.empty(rows, H * D, dtype=torch.bfloat16, device=cuda)
+    assert ops.attn_tc_usable(qn, out, D)
+    ops.attn_prefill_tc(qn, out, kp, vp, table, dev(tile_seq), dev(tile_q0), len(tile_seq), dev(row0), dev(starts), dev(lens),
+                        H, G, D, tile_rows, hpc, chunks, 0, scale, linear._err_word(cuda), None, None, block, sink.to(cuda), gate, 0)
+    plain_kernel = torch.empty_like(out)
+    ops.window_attention(qn, kp, vp, table, a["row_seq"], a["row_pos"], None, None, gate, 0, plain_kernel, H, G, D, D, 0, scale,
+                         chunk=block, sink=sink.to(cuda), gate_per_head=True)
+    linear.check_errors()
+    for got, what in ((out, "tensor cores"), (plain_kernel, "plain kernel")):
+        err = float((got.cpu().double() - ref).abs().max())
+        assert err < 3e-2, f"{what}: {err}"
+
+
 def test_sink_alone_takes_its_share(cuda):
     """One key of score zero and a sink of ln 3: the key's value comes out at a quarter."""
     from camelid_b200.csrc import ops
