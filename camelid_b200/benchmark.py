@@ -531,6 +531,118 @@ def run_fomatar(sizes=("small", "medium"), batch: int = 8, prompt_tokens: int = 
     return out
 
 
+ZULOZEN_SIZES = {
+    # width, layers (dense and routed feed-forwards in turn), feed-forward size of the dense layers, heads of `head`
+    # channels, block of positions a query sees, experts / choices / expert size / shared expert size of the routed
+    # layers (choices * expert + shared = ff: a token passes as many feed-forward elements as in a dense layer)
+    "small": dict(width=1024, layers=8, ff=4096, heads=8, kv_heads=2, head=128, block=512, experts=16, top=2, expert_ff=1024,
+                  shared_ff=2048, vocab=32768),
+    "medium": dict(width=2048, layers=16, ff=8192, heads=16, kv_heads=4, head=128, block=1024, experts=32, top=4, expert_ff=1536,
+                   shared_ff=2048, vocab=32768),
+    "wide": dict(width=4096, layers=8, ff=14336, heads=32, kv_heads=8, head=128, block=1024, experts=32, top=4, expert_ff=2560,
+                 shared_ff=4096, vocab=32768),
+}
+
+
+def zulozen_config_for(size: str) -> dict:
+    s = ZULOZEN_SIZES[size]
+    mixer = {"dim": s["head"], "vdim": s["head"], "heads": s["heads"], "kv_heads": s["kv_heads"], "mask": {"size": s["block"]},
+             "rot": {"dims": s["head"] // 2, "base": 10000.0}, "scale": s["head"] ** -0.5}
+    layers = []
+    for i in range(s["layers"]):
+        mlp = ({"kind": "dense", "ff": s["ff"]} if i % 2 == 0 else
+               {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "router": {"experts": s["experts"], "top": s["top"]},
+                "shared": {"ff": s["shared_ff"]}})
+        layers.append({"type": "attention", "mixer": dict(mixer), "mlp": mlp})
+    return {"architecture": "Zulozen", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.3,
+            "layers": layers}
+
+
+def llama_config_like_zulozen(size: str) -> dict:
+    """The dense Llama decoder of the same width, depth, heads, feed-forward size and vocabulary."""
+    s = ZULOZEN_SIZES[size]
+    return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "max_position_embeddings": 131072,
+            "num_hidden_layers": s["layers"], "hidden_size": s["width"], "num_attention_heads": s["heads"],
+            "num_key_value_heads": s["kv_heads"], "head_dim": s["head"], "intermediate_size": s["ff"],
+            "vocab_size": s["vocab"], "rope_theta": 500000.0, "rope_scaling": None, "rms_norm_eps": 1e-6,
+            "tie_word_embeddings": False}
+
+
+def zulozen_step_bytes(cfg: dict, batch: int, context: float, elem: int) -> dict:
+    """Bytes a decode step must move: every matrix a row passes once (of the routed experts those that ``batch`` rows
+    with ``top`` choices can reach at most, the output head, no embedding table), and the keys and values of each
+    sequence's running block of positions."""
+    W = cfg["width"]
+    weights = kv = 0
+    for L in cfg["layers"]:
+        m, f = L["mixer"], L["mlp"]
+        weights += W * (m["heads"] * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"]) + m["heads"]) + m["heads"] * m["vdim"] * W
+        if f and f["kind"] == "dense":
+            weights += 2 * W * f["ff"]
+        elif f:
+            reach = min(f["router"]["experts"], batch * f["router"]["top"])
+            weights += W * f["router"]["experts"] + 3 * W * (reach * f["expert"]["ff"] + (f.get("shared") or {"ff": 0})["ff"])
+        seen = min(context, (context % m["mask"]["size"]) + 1) if m.get("mask") else context
+        kv += batch * seen * m["kv_heads"] * (m["dim"] + m["vdim"])
+    weights += cfg["vocab"] * W
+    return {"weights": int(weights * elem), "kv": int(kv * elem), "state": 0, "total": int((weights + kv) * elem)}
+
+
+def zulozen_prefill_flops(cfg: dict, tokens: int) -> float:
+    """2 x tokens x (elements of every matrix a token passes: of the routed experts its ``top`` choices and the shared
+    one) plus the attention over the keys of each query's own block of positions."""
+    W = cfg["width"]
+    total = 0.0
+    for L in cfg["layers"]:
+        m, f = L["mixer"], L["mlp"]
+        per = W * (m["heads"] * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"]) + m["heads"]) + m["heads"] * m["vdim"] * W
+        if f and f["kind"] == "dense":
+            per += 2 * W * f["ff"]
+        elif f:
+            per += W * f["router"]["experts"] + 3 * W * (f["router"]["top"] * f["expert"]["ff"] + (f.get("shared") or {"ff": 0})["ff"])
+        total += 2.0 * tokens * per
+        block = m["mask"]["size"] if m.get("mask") else tokens
+        seen = sum((i % block) + 1 for i in range(tokens))
+        total += 2.0 * seen * m["heads"] * (m["dim"] + m["vdim"])
+    return total + 2.0 * W * cfg["vocab"]
+
+
+def run_zulozen(sizes=("small", "medium"), batch: int = 8, prompt_tokens: int = 512, steps: int = 64, warmup: int = 4,
+                prefill_tokens: int = 2048, dtype: str = "bfloat16") -> dict:
+    """Decode steps (timed on the device in the loop ``generate`` runs) and prefill steps of the Zulozen decoder and of
+    the dense Llama decoder of equal width, depth, heads, feed-forward size and vocabulary, random weights."""
+    from . import api
+    pk = peaks()
+    elem = 2 if dtype == "bfloat16" else 4
+    out = {"metric": "decode and prefill tokens/s, Zulozen beside the dense decoder of equal size", "dtype": dtype,
+           "batch": batch, "prompt_tokens": prompt_tokens, "steps": steps, "warmup": warmup,
+           "prefill_tokens": prefill_tokens, "peaks": pk["source"], "data": "synthetic (seeded uniform token ids, random weights)",
+           "sizes": {}}
+    for size in sizes:
+        rec = {"shape": ZULOZEN_SIZES[size]}
+        for label, cfg in (("zulozen", zulozen_config_for(size)), ("llama", llama_config_like_zulozen(size))):
+            lm = api.from_random(cfg, seed=7, dtype=dtype)
+            vocab = {"vocab_size": ZULOZEN_SIZES[size]["vocab"]}
+            rng = np.random.default_rng(7)
+            dec = measure_decode_device(lm, vocab, batch, prompt_tokens, steps, warmup, rng)
+            bytes_step = (zulozen_step_bytes(cfg, batch, dec["context"], elem) if label == "zulozen"
+                          else model_step_bytes(lm, batch, dec["context"]))
+            pre = measure_prefill(lm, vocab, prefill_tokens, rng)
+            flops = zulozen_prefill_flops(cfg, prefill_tokens) if label == "zulozen" else prefill_flops(cfg, prefill_tokens)
+            together = _prefill_together(lm, _prompts(rng, batch, prompt_tokens, vocab["vocab_size"]))
+            rec[label] = {
+                "decode_tokens_per_s": dec["value"], "decode_ms_per_step": dec["ms_per_step"], "launches_per_step": dec["launches"] / steps,
+                "decode_bytes": bytes_step, "decode_frac_of_copy": bytes_step["total"] / (dec["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"],
+                "prefill_tokens_per_s": pre["value"], "prefill_ms": pre["ms"], "prefill_flops": flops,
+                "prefill_batch_tokens_per_s": together["value"], "prefill_batch_ms": together["ms"],
+                "prefill_frac_of_gemm": flops / (pre["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12) if dtype == "bfloat16" else None,
+                "clocks": dec["clocks"]}
+            del lm
+            torch.cuda.empty_cache()
+        out["sizes"][size] = rec
+    return out
+
+
 def ablate_decode(batch: int = 8, prompt_tokens: int = 2048, dtype: str = "bfloat16", layers: int | None = None,
                   config_index: int = 2, reps: int = 50) -> dict:
     """Where a decode step's time goes: the captured step graph is timed whole, and again with

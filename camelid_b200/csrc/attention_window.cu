@@ -103,12 +103,19 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const float* __restric
                                    const int* __restrict__ table, int max_blocks, T* __restrict__ q_out, T* __restrict__ k_pages,
                                    T* __restrict__ v_pages, int heads, int kv_heads, int D, int Dv) {
     __shared__ float red[33];
+    __shared__ float2 turn[128];                                // (cosine, sine) of the row's angles, shared by all heads
     pdl_wait();
     pdl_launch_dependents();
     const int r = blockIdx.x;
     const float* x = proj + (size_t)r * ld;
     const int qw = heads * D, kw = kv_heads * D, vw = kv_heads * Dv;
     const int pos = row_pos[r];
+    for (int i = threadIdx.x; i < rot_dim / 2; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        turn[i] = make_float2(cs, sn);
+    }
+    __syncthreads();
     const int page = table[(size_t)row_seq[r] * max_blocks + pos / CML_PAGE];
     float q_scale = 1.0f, k_scale = 1.0f;
     if (norm_mode == 2) {
@@ -144,8 +151,7 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const float* __restric
                     const int c0 = pairing ? 2 * i : i, c1 = pairing ? 2 * i + 1 : i + half;
                     float a = xh[c0], b = xh[c1];
                     if (norm_mode) { a = a * sc * to_f32(w[woff + c0]); b = b * sc * to_f32(w[woff + c1]); }
-                    float sn, cs;
-                    sincosf((float)pos * inv_freq[i], &sn, &cs);
+                    const float cs = turn[i].x, sn = turn[i].y;
                     o[c0] = from_f32<T>(a * cs - b * sn);
                     o[c1] = from_f32<T>(b * cs + a * sn);
                 }
@@ -167,7 +173,7 @@ extern "C" int cml_qkv_prepare(const float* proj, long ld, const void* q_w, cons
                                const int* table, int max_blocks, void* q_out, void* k_pages, void* v_pages, int dtype, int rows,
                                int heads, int kv_heads, int D, int Dv, void* stream) {
     if (rows <= 0) return 0;
-    if (rot_dim < 0 || rot_dim > D || (rot_dim & 1) || norm_mode < 0 || norm_mode > 2) return CML_ERR_BAD_SIZE;
+    if (rot_dim < 0 || rot_dim > D || rot_dim > 256 || (rot_dim & 1) || norm_mode < 0 || norm_mode > 2) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
 #define QP_CASE(T_, TW_, D_, DW_)                                                                                          \
     if (dtype == D_ && w_dtype == DW_) {                                                                                   \

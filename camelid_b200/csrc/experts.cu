@@ -144,7 +144,20 @@ __global__ void expert_gather_kernel(const T* __restrict__ x, long ldx, int widt
     const float w = scale_input ? wts[p] : 1.0f;
     const T* src = x + (size_t)(p / top) * ldx;
     T* dst = xs + (size_t)pos * width;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = scale_input ? from_f32<T>(to_f32(src[c]) * w) : src[c];
+    constexpr int VEC = 16 / (int)sizeof(T);
+    if (width % VEC == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {          // rows in 16-byte pieces
+        for (int c = threadIdx.x * VEC; c < width; c += blockDim.x * VEC) {
+            union { uint4 raw; T e[VEC]; } v;
+            v.raw = *reinterpret_cast<const uint4*>(src + c);
+            if (scale_input) {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) v.e[k] = from_f32<T>(to_f32(v.e[k]) * w);
+            }
+            *reinterpret_cast<uint4*>(dst + c) = v.raw;
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = scale_input ? from_f32<T>(to_f32(src[c]) * w) : src[c];
+    }
     if (threadIdx.x == 0) pos_of_pair[p] = pos;
 }
 
@@ -265,6 +278,23 @@ __global__ void expert_combine_kernel(const float* __restrict__ y, const int* __
     pdl_wait();
     pdl_launch_dependents();
     const int r = blockIdx.x;
+    if ((hidden & 3) == 0) {                                    // four columns a thread, 16-byte accesses
+        for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < shared_splits; ++s) {
+                const float4 t = *reinterpret_cast<const float4*>(shared + (size_t)s * shared_stride + (size_t)r * hidden + c);
+                v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+            }
+            for (int k = 0; k < top; ++k) {
+                const int p = r * top + k;
+                const float4 t = *reinterpret_cast<const float4*>(y + (size_t)pos_of_pair[p] * hidden + c);
+                const float w = scale_output ? wts[p] : 1.0f;
+                v.x += t.x * w; v.y += t.y * w; v.z += t.z * w; v.w += t.w * w;
+            }
+            *reinterpret_cast<float4*>(out + (size_t)r * hidden + c) = v;
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         float v = 0.f;
         for (int s = 0; s < shared_splits; ++s) v += shared[(size_t)s * shared_stride + (size_t)r * hidden + c];

@@ -98,6 +98,8 @@ _SIGNATURES = {
     ("token_ops", "cml_bias_act"): [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
     ("token_ops", "cml_gate_rows"): [c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p],
     ("token_ops", "cml_softcap"): [c_void_p, c_long, c_float, c_void_p],
+    ("token_ops", "cml_post_norm_add"): [c_void_p, c_int, c_long, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_void_p,
+                                         c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     ("token_ops", "cml_norm_combine"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                                         c_float, c_float, c_void_p],
     ("recurrence", "cml_conv_unit"): [c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -477,6 +479,27 @@ def norm_combine(branches: list, residual: torch.Tensor, eps: float, coef: float
         ys[i], ws[i], splits[i], strides[i] = y.data_ptr(), w.data_ptr(), y.shape[0], y.stride(0)
     _check(_fn("token_ops", "cml_norm_combine")(ys, ws, bs, splits, strides, n, dtype_code(branches[0][1].dtype), _p(residual),
                                                 rows, hidden, float(eps), float(coef), _stream()), "norm_combine")
+
+
+def post_norm_add(y: torch.Tensor, bias, w_post: torch.Tensor, eps: float, coef: float, residual: torch.Tensor,
+                  w_next=None, eps_next: float = 0.0, x_out=None):
+    """residual[r] += coef * rmsnorm(y[r] + bias) * w_post, and with ``x_out`` also x_out[r] = rmsnorm(residual[r]) * w_next
+    (the norm before the next sublayer) in the same pass. y float32 [rows, hidden] or split sums [splits, rows, hidden]."""
+    _dev(y, bias, w_post, residual, w_next, x_out)
+    rows, hidden = residual.shape
+    if y.dim() == 2:
+        y = y.unsqueeze(0)
+    assert residual.dtype == torch.float32 and residual.is_contiguous()
+    assert y.dtype == torch.float32 and y.shape[1:] == (rows, hidden) and y.stride(2) == 1 and y.stride(1) == hidden
+    assert w_post.numel() == hidden and w_post.is_contiguous()
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == hidden and bias.is_contiguous())
+    if x_out is not None:
+        assert w_next is not None and w_next.dtype == w_post.dtype and w_next.numel() == hidden and w_next.is_contiguous()
+        assert x_out.shape == (rows, hidden) and x_out.is_contiguous()
+    _check(_fn("token_ops", "cml_post_norm_add")(
+        _p(y), y.shape[0], y.stride(0), _p(bias), _p(w_post), dtype_code(w_post.dtype), float(eps), float(coef), _p(residual),
+        _p(w_next), float(eps_next), _p(x_out), dtype_code(x_out.dtype) if x_out is not None else 0, rows, hidden, _stream()),
+        "post_norm_add")
 
 
 # ---------------------------------------------------------------------------------------

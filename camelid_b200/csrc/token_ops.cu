@@ -317,14 +317,24 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     return v;
 }
 
-// x[r, c] = act(x[r, c] + bias[c]) in place (bias float or null).
-template <typename T>
+// x[r, c] = act(x[r, c] + bias[c]) in place (bias float or null). Rows whose size and address allow it go in
+// 16-byte pieces (VEC elements a thread), anything else element by element.
+template <typename T, int VEC>
 __global__ void bias_act_kernel(T* __restrict__ x, const float* __restrict__ bias, long n, int width, int act) {
     pdl_wait();
     pdl_launch_dependents();
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
-        const float b = bias ? bias[i % width] : 0.f;
-        x[i] = from_f32<T>(apply_act(to_f32(x[i]) + b, act));
+    for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i < n; i += (long)gridDim.x * blockDim.x * VEC) {
+        if (VEC == 1) {
+            const float b = bias ? bias[i % width] : 0.f;
+            x[i] = from_f32<T>(apply_act(to_f32(x[i]) + b, act));
+        } else {
+            const int c0 = (int)(i % width);
+            union { uint4 raw; T e[VEC]; } v;
+            v.raw = *reinterpret_cast<const uint4*>(x + i);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) v.e[k] = from_f32<T>(apply_act(to_f32(v.e[k]) + (bias ? bias[c0 + k] : 0.f), act));
+            *reinterpret_cast<uint4*>(x + i) = v.raw;
+        }
     }
 }
 
@@ -332,10 +342,17 @@ extern "C" int cml_bias_act(void* x, int dtype, const float* bias, int rows, int
     const long n = (long)rows * width;
     if (n <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int grid = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
-    if (dtype == CML_DTYPE_F32) launch_pdl(bias_act_kernel<float>, dim3(grid), dim3(256), 0, s, (float*)x, bias, n, width, act);
-    else if (dtype == CML_DTYPE_BF16) launch_pdl(bias_act_kernel<bf16>, dim3(grid), dim3(256), 0, s, (bf16*)x, bias, n, width, act);
-    else return CML_ERR_BAD_DTYPE;
+    const int vec = dtype == CML_DTYPE_F32 ? 4 : 8;
+    const bool wide = width % vec == 0 && ((uintptr_t)x & 15) == 0;
+    const long items = wide ? n / vec : n;
+    const int grid = (int)((items + 255) / 256 < 16384 ? (items + 255) / 256 : 16384);
+    if (dtype == CML_DTYPE_F32) {
+        if (wide) launch_pdl(bias_act_kernel<float, 4>, dim3(grid), dim3(256), 0, s, (float*)x, bias, n, width, act);
+        else launch_pdl(bias_act_kernel<float, 1>, dim3(grid), dim3(256), 0, s, (float*)x, bias, n, width, act);
+    } else if (dtype == CML_DTYPE_BF16) {
+        if (wide) launch_pdl(bias_act_kernel<bf16, 8>, dim3(grid), dim3(256), 0, s, (bf16*)x, bias, n, width, act);
+        else launch_pdl(bias_act_kernel<bf16, 1>, dim3(grid), dim3(256), 0, s, (bf16*)x, bias, n, width, act);
+    } else return CML_ERR_BAD_DTYPE;
     return cml_launch_status();
 }
 
@@ -527,4 +544,102 @@ extern "C" int cml_norm_combine(const float* const* y, const void* const* w, con
     } else
         return CML_ERR_BAD_DTYPE;
     return cml_launch_status();
+}
+
+// ------------------------------------------------------------------------------------
+// The norm behind a sublayer and, where wanted, the norm before the next one, in one pass over a row:
+//   v = sum over splits of y[split][r] + bias;   h[r] += coef * v / sqrt(mean(v^2) + eps) * w_post;
+//   x_out[r] = h[r] / sqrt(mean(h[r]^2) + eps_next) * w_next     (if x_out is given)
+// One block per row; the row stays in shared memory between the passes; all sums in float.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256) post_norm_add_kernel(const float* __restrict__ y, int n_splits, long split_stride,
+                                                            const float* __restrict__ bias, const TW* __restrict__ w_post,
+                                                            float eps, float coef, float* __restrict__ h,
+                                                            const TW* __restrict__ w_next, float eps_next,
+                                                            TO* __restrict__ x_out, int hidden) {
+    extern __shared__ __align__(16) float pn_row[];
+    __shared__ float red[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t base = (size_t)blockIdx.x * hidden;
+    const bool vec = (hidden & 3) == 0;
+    float ss = 0.f;
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+            float4 v = *reinterpret_cast<const float4*>(y + base + c);
+            for (int s = 1; s < n_splits; ++s) {
+                const float4 t = *reinterpret_cast<const float4*>(y + (size_t)s * split_stride + base + c);
+                v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+            }
+            if (bias) { v.x += bias[c]; v.y += bias[c + 1]; v.z += bias[c + 2]; v.w += bias[c + 3]; }
+            *reinterpret_cast<float4*>(pn_row + c) = v;
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            float v = y[base + c];
+            for (int s = 1; s < n_splits; ++s) v += y[(size_t)s * split_stride + base + c];
+            if (bias) v += bias[c];
+            pn_row[c] = v;
+            ss = fmaf(v, v, ss);
+        }
+    }
+    const float s1 = coef / sqrtf(block_sum(ss, red) / (float)hidden + eps);
+    __syncthreads();
+    float ss2 = 0.f;
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(pn_row + c);
+            float4 o = *reinterpret_cast<const float4*>(h + base + c);
+            o.x += v.x * s1 * to_f32(w_post[c]); o.y += v.y * s1 * to_f32(w_post[c + 1]);
+            o.z += v.z * s1 * to_f32(w_post[c + 2]); o.w += v.w * s1 * to_f32(w_post[c + 3]);
+            *reinterpret_cast<float4*>(h + base + c) = o;
+            *reinterpret_cast<float4*>(pn_row + c) = o;
+            ss2 = fmaf(o.x, o.x, fmaf(o.y, o.y, fmaf(o.z, o.z, fmaf(o.w, o.w, ss2))));
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float o = h[base + c] + pn_row[c] * s1 * to_f32(w_post[c]);
+            h[base + c] = o;
+            pn_row[c] = o;
+            ss2 = fmaf(o, o, ss2);
+        }
+    }
+    if (x_out == nullptr) return;
+    const float s2 = 1.0f / sqrtf(block_sum(ss2, red) / (float)hidden + eps_next);
+    if (!vec) {                                                   // each thread reads back what it wrote itself
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) x_out[base + c] = from_f32<TO>(pn_row[c] * s2 * to_f32(w_next[c]));
+    } else {
+        for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+            const float4 o = *reinterpret_cast<const float4*>(pn_row + c);
+            x_out[base + c] = from_f32<TO>(o.x * s2 * to_f32(w_next[c]));
+            x_out[base + c + 1] = from_f32<TO>(o.y * s2 * to_f32(w_next[c + 1]));
+            x_out[base + c + 2] = from_f32<TO>(o.z * s2 * to_f32(w_next[c + 2]));
+            x_out[base + c + 3] = from_f32<TO>(o.w * s2 * to_f32(w_next[c + 3]));
+        }
+    }
+}
+
+extern "C" int cml_post_norm_add(const float* y, int n_splits, long split_stride, const float* bias, const void* w_post, int w_dtype,
+                                 float eps, float coef, float* h, const void* w_next, float eps_next, void* x_out, int out_dtype,
+                                 int rows, int hidden, void* stream) {
+    if (rows <= 0) return 0;
+    if (n_splits < 1) return CML_ERR_BAD_SIZE;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int block = hidden >= 1024 ? 256 : 128;
+#define PN_CASE(TW_, TO_, DW_, DO_)                                                                                        \
+    if (w_dtype == DW_ && (x_out == nullptr || out_dtype == DO_)) {                                                        \
+        if (smem > 48 * 1024 && cml_allow_smem<post_norm_add_kernel<TW_, TO_>>(smem) != cudaSuccess) return CML_ERR_BAD_SIZE; \
+        launch_pdl(post_norm_add_kernel<TW_, TO_>, dim3(rows), dim3(block), smem, s, y, n_splits, split_stride, bias,     \
+                   (const TW_*)w_post, eps, coef, h, (const TW_*)w_next, eps_next, (TO_*)x_out, hidden);                   \
+        return cml_launch_status();                                                                                        \
+    }
+    PN_CASE(bf16, bf16, CML_DTYPE_BF16, CML_DTYPE_BF16)
+    PN_CASE(float, float, CML_DTYPE_F32, CML_DTYPE_F32)
+    PN_CASE(float, bf16, CML_DTYPE_F32, CML_DTYPE_BF16)
+    PN_CASE(bf16, float, CML_DTYPE_BF16, CML_DTYPE_F32)
+#undef PN_CASE
+    return CML_ERR_BAD_DTYPE;
 }

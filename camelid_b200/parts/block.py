@@ -128,8 +128,10 @@ class SandwichBlock(Part):
     def forward(self, ctx, h):
         ctx.settle(h)                       # whatever a layer of another arrangement left undone
         x = self.norm1.forward(ctx, h)
-        self.post1.add_normed(ctx, self.mixer.branch_output(ctx, x, "mixer_out"), h, self.scale)
+        # the norm behind the mixer and the one before the feed-forward share a pass over the rows where they can
+        x = self.post1.add_normed(ctx, self.mixer.branch_output(ctx, x, "mixer_out"), h, self.scale, None, then=self.norm2)
         if self.ffn is not None:
-            x = self.norm2.forward(ctx, h)
+            if x is None:
+                x = self.norm2.forward(ctx, h)
             y, bias = self.ffn.output(ctx, x, "ffn_out")
             self.post2.add_normed(ctx, y, h, self.scale, bias)

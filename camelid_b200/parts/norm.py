@@ -47,7 +47,14 @@ class RMSNorm(Part):
         ops.rmsnorm(h, self.weight, self.eps, out, rows_index, pending)
         return out
 
-    def add_normed(self, ctx, y, residual, scale: float = 1.0, bias=None) -> None:
+    def add_normed(self, ctx, y, residual, scale: float = 1.0, bias=None, then=None, name="normed"):
         """residual += scale * rmsnorm(y + bias) * w: this norm on a sublayer's output rows ``y`` (float32
-        [rows, hidden], or split sums [splits, rows, hidden] that are added first), added into the stream."""
-        ops.norm_combine([(y, self.weight)], residual, self.eps, scale, [bias])
+        [rows, hidden], or split sums [splits, rows, hidden] that are added first), added into the stream.
+        ``then``: the norm part that reads the stream next; if it is one of this kind, its rows come out of the
+        same pass and are returned (else None: the caller runs that norm itself)."""
+        fuse = (isinstance(then, RMSNorm) and then.weight is not None and then.weight.dtype == self.weight.dtype
+                and then.hidden_size == self.hidden_size)
+        x = ctx.buffer(name, (residual.shape[0], self.hidden_size)) if fuse else None
+        ops.post_norm_add(y, bias, self.weight, self.eps, scale, residual, then.weight if fuse else None,
+                          then.eps if fuse else 0.0, x)
+        return x
