@@ -95,9 +95,12 @@ extern "C" int cml_qk_norm_kv_write(const float* proj, long ld, const void* q_w,
 // they are; 1: RMS norm per head, weights of D channels shared by the heads; 2: RMS norm over the whole q
 // projection (heads x D channels at once) and the whole k projection, weights of those sizes. Then the first
 // rot_dim channels of every q and k head are rotated by angle = position * inv_freq[i] (float), pairing 1:
-// channels (2i, 2i + 1); pairing 0: channels (i, i + rot_dim / 2). One block per row.
+// channels (2i, 2i + 1); pairing 0: channels (i, i + rot_dim / 2). One block per row. proj may come as split sums
+// (n_splits matrices split_stride apart, added here in split order); the row is staged in shared memory. `extra`
+// more columns behind v (the logits of an output gate) are copied, summed, to extra_out [rows, extra].
 template <typename T, typename TW>
-__global__ void __launch_bounds__(256) qkv_prepare_kernel(const float* __restrict__ proj, long ld, const TW* __restrict__ q_w,
+__global__ void __launch_bounds__(1024) qkv_prepare_kernel(const float* __restrict__ proj, long ld, int n_splits, long split_stride,
+                                   int extra, float* __restrict__ extra_out, const TW* __restrict__ q_w,
                                    const TW* __restrict__ k_w, int norm_mode, float eps, const float* __restrict__ inv_freq,
                                    int rot_dim, int pairing, const int* __restrict__ row_seq, const int* __restrict__ row_pos,
                                    const int* __restrict__ table, int max_blocks, T* __restrict__ q_out, T* __restrict__ k_pages,
@@ -106,9 +109,27 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const float* __restric
     __shared__ float2 turn[128];                                // (cosine, sine) of the row's angles, shared by all heads
     pdl_wait();
     pdl_launch_dependents();
+    extern __shared__ __align__(16) float x[];                 // the row: q, k, v and the extra columns
     const int r = blockIdx.x;
-    const float* x = proj + (size_t)r * ld;
     const int qw = heads * D, kw = kv_heads * D, vw = kv_heads * Dv;
+    {
+        const float* src = proj + (size_t)r * ld;
+        const int total = qw + kw + vw + extra;
+        for (int c = threadIdx.x; c < total; c += blockDim.x) {
+            // eight splits at a time: the loads are unconditional (of a valid place) and all in flight before the
+            // first add; the adds stay in split order
+            float v = 0.f;
+            for (int s0 = 0; s0 < n_splits; s0 += 8) {
+                float t[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) t[k] = src[(size_t)min(s0 + k, n_splits - 1) * split_stride + c];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v += s0 + k < n_splits ? t[k] : 0.f;
+            }
+            x[c] = v;
+            if (c >= total - extra) extra_out[(size_t)r * extra + (c - (total - extra))] = v;
+        }
+    }
     const int pos = row_pos[r];
     for (int i = threadIdx.x; i < rot_dim / 2; i += blockDim.x) {
         float sn, cs;
@@ -168,16 +189,21 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const float* __restric
     }
 }
 
-extern "C" int cml_qkv_prepare(const float* proj, long ld, const void* q_w, const void* k_w, int w_dtype, int norm_mode, float eps,
+extern "C" int cml_qkv_prepare(const float* proj, long ld, int n_splits, long split_stride, int extra, float* extra_out, const void* q_w, const void* k_w, int w_dtype, int norm_mode, float eps,
                                const float* inv_freq, int rot_dim, int pairing, const int* row_seq, const int* row_pos,
                                const int* table, int max_blocks, void* q_out, void* k_pages, void* v_pages, int dtype, int rows,
                                int heads, int kv_heads, int D, int Dv, void* stream) {
     if (rows <= 0) return 0;
     if (rot_dim < 0 || rot_dim > D || rot_dim > 256 || (rot_dim & 1) || norm_mode < 0 || norm_mode > 2) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    if (n_splits < 1 || extra < 0) return CML_ERR_BAD_SIZE;
+    const size_t smem = (size_t)(heads * D + kv_heads * (D + Dv) + extra) * sizeof(float);
+    if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
 #define QP_CASE(T_, TW_, D_, DW_)                                                                                          \
     if (dtype == D_ && w_dtype == DW_) {                                                                                   \
-        launch_pdl(qkv_prepare_kernel<T_, TW_>, dim3(rows), dim3(256), 0, s, proj, ld, (const TW_*)q_w, (const TW_*)k_w,   \
+        if (smem > 48 * 1024 && cml_allow_smem<qkv_prepare_kernel<T_, TW_>>(smem) != cudaSuccess) return CML_ERR_BAD_SIZE; \
+        launch_pdl(qkv_prepare_kernel<T_, TW_>, dim3(rows), dim3(rows <= 128 ? 1024 : 256), smem, s, proj, ld, n_splits, split_stride, extra,   \
+                   extra_out, (const TW_*)q_w, (const TW_*)k_w,                                                            \
                    norm_mode, eps, inv_freq, rot_dim, pairing, row_seq, row_pos, table, max_blocks, (T_*)q_out,            \
                    (T_*)k_pages, (T_*)v_pages, heads, kv_heads, D, Dv);                                                    \
         return cml_launch_status();                                                                                        \

@@ -19,13 +19,28 @@
 
 // One warp per row. A lane looks after experts lane, lane + 32, ...; a chosen expert is marked in the lane's
 // bit mask (so at most 1,024 experts). Ties go to the lower index.
-__global__ void route_topk_kernel(const float* __restrict__ logits, long ld, int rows, int E, int top, int score_mode,
-                                  int renorm, int* __restrict__ ids, float* __restrict__ wts) {
+// The logits may come as split sums (n_splits matrices split_stride apart): a warp adds them, in split order, into its
+// own stretch of shared memory first (E floats a warp).
+__global__ void route_topk_kernel(const float* __restrict__ logits, long ld, int n_splits, long split_stride, int rows, int E,
+                                  int top, int score_mode, int renorm, int* __restrict__ ids, float* __restrict__ wts) {
+    extern __shared__ float rt_z[];
     pdl_wait();
     pdl_launch_dependents();
     const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (r >= rows) return;
-    const float* z = logits + (size_t)r * ld;
+    float* z = rt_z + (threadIdx.x >> 5) * E;
+    for (int e = lane; e < E; e += 32) {
+        float v = 0.f;
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {              // eight splits' loads in flight, added in split order
+            float t[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) t[k] = logits[(size_t)min(s0 + k, n_splits - 1) * split_stride + (size_t)r * ld + e];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v += s0 + k < n_splits ? t[k] : 0.f;
+        }
+        z[e] = v;
+    }
+    __syncwarp();
     float zmax = -INFINITY, zsum = 0.f;
     if (score_mode == 1) {
         for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
@@ -60,12 +75,12 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, long ld, int
     }
 }
 
-extern "C" int cml_route_topk(const float* logits, long ld, int rows, int E, int top, int score_mode, int renorm, int* ids,
-                              float* wts, void* stream) {
+extern "C" int cml_route_topk(const float* logits, long ld, int n_splits, long split_stride, int rows, int E, int top,
+                              int score_mode, int renorm, int* ids, float* wts, void* stream) {
     if (rows <= 0) return 0;
-    if (E < 1 || E > 1024 || top < 1 || top > E) return CML_ERR_BAD_SIZE;
-    launch_pdl(route_topk_kernel, dim3((rows + 3) / 4), dim3(128), 0, (cudaStream_t)stream, logits, ld, rows, E, top, score_mode,
-               renorm, ids, wts);
+    if (E < 1 || E > 1024 || top < 1 || top > E || n_splits < 1) return CML_ERR_BAD_SIZE;
+    launch_pdl(route_topk_kernel, dim3((rows + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), (cudaStream_t)stream, logits, ld,
+               n_splits, split_stride, rows, E, top, score_mode, renorm, ids, wts);
     return cml_launch_status();
 }
 

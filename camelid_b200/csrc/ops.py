@@ -119,10 +119,11 @@ _SIGNATURES = {
     ("attention_window", "cml_window_attention"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                                    c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int,
                                                    c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p],
-    ("attention_window", "cml_qkv_prepare"): [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int,
+    ("attention_window", "cml_qkv_prepare"): [c_void_p, c_long, c_int, c_long, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int,
                                               c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                               c_int, c_int, c_int, c_int, c_void_p],
-    ("experts", "cml_route_topk"): [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ("experts", "cml_route_topk"): [c_void_p, c_long, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                    c_void_p],
     ("experts", "cml_expert_plan"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     ("gemm_tc", "cml_gemm_tc_grouped"): [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_long, c_int,
                                          c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -635,15 +636,21 @@ def window_attention(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate,
 
 
 def qkv_prepare(proj: torch.Tensor, q_w, k_w, norm_mode: int, eps: float, inv_freq, rotary_dim: int, interleaved: bool,
-                row_seq, row_pos, table, q_out, k_pages, v_pages, heads: int, kv_heads: int, key_dim: int, value_dim: int):
-    """From ``proj`` (float32 rows: q, k, v): RMS norm of q and k (``norm_mode`` 0 none, 1 per head with weights
+                row_seq, row_pos, table, q_out, k_pages, v_pages, heads: int, kv_heads: int, key_dim: int, value_dim: int,
+                extra_out=None):
+    """From ``proj`` (float32 rows: q, k, v; [rows, n] or split sums [splits, rows, n], added here): RMS norm of q and k (``norm_mode`` 0 none, 1 per head with weights
     [key_dim], 2 over the whole projection with weights [heads * key_dim] and [kv_heads * key_dim]), then the
     first ``rotary_dim`` channels of every head rotated by position * inv_freq (pairs of neighbours if
-    ``interleaved``, else of the two halves); q to ``q_out``, k and v into their pages, in the compute type."""
-    _dev(proj, q_w, k_w, inv_freq, row_seq, row_pos, table, q_out, k_pages, v_pages)
+    ``interleaved``, else of the two halves); q to ``q_out``, k and v into their pages, in the compute type.
+    ``extra_out`` (float32 [rows, e]): the e columns behind v (an output gate's logits), summed over the splits."""
+    _dev(proj, q_w, k_w, inv_freq, row_seq, row_pos, table, q_out, k_pages, v_pages, extra_out)
     rows = q_out.shape[0]
-    assert proj.dtype == torch.float32 and proj.stride(1) == 1
-    assert proj.shape[1] >= heads * key_dim + kv_heads * (key_dim + value_dim)
+    if proj.dim() == 2:
+        proj = proj.unsqueeze(0)
+    assert proj.dtype == torch.float32 and proj.stride(2) == 1 and proj.shape[1] == rows
+    extra = extra_out.shape[1] if extra_out is not None else 0
+    assert extra_out is None or (extra_out.dtype == torch.float32 and extra_out.is_contiguous() and extra_out.shape[0] == rows)
+    assert proj.shape[2] >= heads * key_dim + kv_heads * (key_dim + value_dim) + extra
     assert q_out.is_contiguous() and q_out.shape[1] == heads * key_dim and k_pages.dtype == q_out.dtype == v_pages.dtype
     assert k_pages.is_contiguous() and v_pages.is_contiguous()
     assert k_pages.shape[1:] == (kv_heads, PAGE, key_dim) and v_pages.shape[1:] == (kv_heads, PAGE, value_dim)
@@ -653,7 +660,7 @@ def qkv_prepare(proj: torch.Tensor, q_w, k_w, norm_mode: int, eps: float, inv_fr
     if rotary_dim:
         assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2
     _check(_fn("attention_window", "cml_qkv_prepare")(
-        _p(proj), proj.stride(0), _p(q_w), _p(k_w), dtype_code(q_w.dtype) if norm_mode else dtype_code(q_out.dtype), int(norm_mode),
+        _p(proj), proj.stride(1), proj.shape[0], proj.stride(0), extra, _p(extra_out), _p(q_w), _p(k_w), dtype_code(q_w.dtype) if norm_mode else dtype_code(q_out.dtype), int(norm_mode),
         float(eps), _p(inv_freq), int(rotary_dim), 1 if interleaved else 0, _p(row_seq), _p(row_pos), _p(table), table.shape[1],
         _p(q_out), _p(k_pages), _p(v_pages), dtype_code(q_out.dtype), rows, heads, kv_heads, key_dim, value_dim, _stream()),
         "qkv_prepare")
@@ -664,12 +671,15 @@ def qkv_prepare(proj: torch.Tensor, q_w, k_w, norm_mode: int, eps: float, inv_fr
 
 def route_topk(logits: torch.Tensor, top: int, softmax: bool, renorm: bool, ids: torch.Tensor, wts: torch.Tensor):
     """The ``top`` largest logits of every row: their expert ids and weights (sigmoid of the logit, or its softmax
-    over all experts; ``renorm``: divided by the chosen weights' sum). logits float32 [rows, experts]."""
+    over all experts; ``renorm``: divided by the chosen weights' sum). logits float32 [rows, experts], or split sums
+    [splits, rows, experts] that are added first."""
     _dev(logits, ids, wts)
-    rows, experts = logits.shape
-    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and ids.dtype == torch.int32 and wts.dtype == torch.float32
+    if logits.dim() == 2:
+        logits = logits.unsqueeze(0)
+    _, rows, experts = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(2) == 1 and ids.dtype == torch.int32 and wts.dtype == torch.float32
     assert ids.numel() == rows * top == wts.numel() and ids.is_contiguous() and wts.is_contiguous()
-    _check(_fn("experts", "cml_route_topk")(_p(logits), logits.stride(0), rows, experts, int(top), 1 if softmax else 0,
+    _check(_fn("experts", "cml_route_topk")(_p(logits), logits.stride(1), logits.shape[0], logits.stride(0), rows, experts, int(top), 1 if softmax else 0,
                                             1 if renorm else 0, _p(ids), _p(wts), _stream()), "route_topk")
 
 

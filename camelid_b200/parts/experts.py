@@ -86,7 +86,7 @@ class RoutedExperts(Part):
         rows, top, E = x.shape[0], self.top, self.experts
         pairs = rows * top
         i32 = lambda n, k: ctx.buffer(f"{name}_{n}", (k,), torch.int32)        # noqa: E731
-        logits = linear.product_rows_f32(ctx, x, self.w_router, name + "_router")
+        logits = linear.product_f32(ctx, x, self.w_router, name + "_router")          # split sums where the step has few rows
         ids, wts = i32("ids", pairs), ctx.buffer(name + "_wts", (pairs,), torch.float32)
         ops.route_topk(logits, top, self.scoring == "softmax", self.renormalize, ids, wts)
         rank, counts, offsets, tile_first = i32("rank", pairs), i32("counts", E), i32("offsets", E + 1), i32("tiles", E + 1)

@@ -132,15 +132,20 @@ class WindowAttention(Part):
         n = ctx.n_rows
         group, k_pages, v_pages = ctx.kv()
         table = ctx.block_table(group)
-        if proj is None:
-            proj = linear.product_rows_f32(ctx, x, self.w_in, "wa_proj")
         q = ctx.buffer("wa_q", (n, self.q_width))
         if self.prepare:
+            # the product's split sums (few rows) are added by the preparing kernel, which also hands the gate's logits on
             pos = self.position
-            ops.qkv_prepare(proj, self.q_w, self.k_w, {None: 0, "head": 1, "full": 2}[self.qk_norm], self.eps, pos.inv_freq,
+            sums = proj if proj is not None else linear.product_f32(ctx, x, self.w_in, "wa_proj")
+            proj = ctx.buffer("wa_gate", (n, self.gate_width), torch.float32) if self.output_gate else None
+            ops.qkv_prepare(sums, self.q_w, self.k_w, {None: 0, "head": 1, "full": 2}[self.qk_norm], self.eps, pos.inv_freq,
                             pos.rotary_dim, pos.pairing == "interleaved", ctx.row_seq, ctx.row_pos, table, q, k_pages, v_pages,
-                            self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim)
+                            self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, proj)
+            gate_col = 0
         else:
+            gate_col = self.gate_col
+            if proj is None:
+                proj = linear.product_rows_f32(ctx, x, self.w_in, "wa_proj")
             ops.qk_norm_kv_write(proj, self.q_w, self.k_w, self.eps, ctx.row_seq, ctx.row_pos, table, q, k_pages, v_pages,
                                  self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim)
         out = ctx.buffer("wa_out", (n, self.o_width))
@@ -152,12 +157,12 @@ class WindowAttention(Part):
             ops.attn_prefill_tc(q, out, k_pages, v_pages, table, tile_seq, tile_q0, n_tiles, ctx.seq_row0, ctx.seq_start,
                                 ctx.seq_new, self.num_heads, self.num_kv_heads, self.head_dim, rows, hpc, chunks,
                                 self.window or 0, self.scale, linear._err_word(q.device), self.r1, self.r2, self.chunk or 0,
-                                self.sink_w, proj if self.output_gate == "head" else None, self.gate_col)
+                                self.sink_w, proj if self.output_gate == "head" else None, gate_col)
             if self.output_gate == "channel":
-                ops.gate_rows_(out, proj, self.gate_col)
+                ops.gate_rows_(out, proj, gate_col)
             return out
         ops.window_attention(q, k_pages, v_pages, table, ctx.row_seq, ctx.row_pos, self.r1, self.r2,
-                             proj if self.output_gate else None, self.gate_col, out, self.num_heads, self.num_kv_heads,
+                             proj if self.output_gate else None, gate_col, out, self.num_heads, self.num_kv_heads,
                              self.head_dim, self.value_dim, self.window or 0, self.scale, self.chunk or 0, self.sink_w,
                              self.output_gate == "head")
         return out
