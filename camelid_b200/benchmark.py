@@ -569,9 +569,9 @@ def llama_config_like_zulozen(size: str) -> dict:
 
 
 def zulozen_step_bytes(cfg: dict, batch: int, context: float, elem: int) -> dict:
-    """Bytes a decode step must move: every matrix a row passes once (of the routed experts those that ``batch`` rows
-    with ``top`` choices can reach at most, the output head, no embedding table), and the keys and values of each
-    sequence's running block of positions."""
+    """Bytes a decode step must move: every matrix a row passes once (of the routed experts as many as ``batch`` rows
+    with ``top`` choices each reach on average when the choices are uniform, E (1 - (1 - top / E)^batch); the output
+    head, no embedding table), and the keys and values of each sequence's running block of positions."""
     W = cfg["width"]
     weights = kv = 0
     for L in cfg["layers"]:
@@ -580,7 +580,7 @@ def zulozen_step_bytes(cfg: dict, batch: int, context: float, elem: int) -> dict
         if f and f["kind"] == "dense":
             weights += 2 * W * f["ff"]
         elif f:
-            reach = min(f["router"]["experts"], batch * f["router"]["top"])
+            reach = f["router"]["experts"] * (1.0 - (1.0 - f["router"]["top"] / f["router"]["experts"]) ** batch)
             weights += W * f["router"]["experts"] + 3 * W * (reach * f["expert"]["ff"] + (f.get("shared") or {"ff": 0})["ff"])
         seen = min(context, (context % m["mask"]["size"]) + 1) if m.get("mask") else context
         kv += batch * seen * m["kv_heads"] * (m["dim"] + m["vdim"])

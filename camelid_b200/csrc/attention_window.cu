@@ -118,8 +118,8 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(const float* __restri
         for (int c = threadIdx.x; c < total; c += blockDim.x) {
             // eight splits at a time: the loads are unconditional (of a valid place) and all in flight before the
             // first add; the adds stay in split order
-            float v = 0.f;
-            for (int s0 = 0; s0 < n_splits; s0 += 8) {
+            float v = src[c];
+            for (int s0 = 1; s0 < n_splits; s0 += 8) {
                 float t[8];
 #pragma unroll
                 for (int k = 0; k < 8; ++k) t[k] = src[(size_t)min(s0 + k, n_splits - 1) * split_stride + c];
@@ -148,36 +148,57 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(const float* __restri
         k_scale = 1.0f / sqrtf(block_sum(sk, red) / (float)kw + eps);
         __syncthreads();
     }
+    float* head_scale = x + qw + kw + vw + extra;               // norm per head: one scale per q and k head
+    if (norm_mode == 1) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+        for (int u = warp; u < heads + kv_heads; u += nwarps) {
+            float ss = 0.f;
+            for (int c = lane; c < D; c += 32) ss = fmaf(x[u * D + c], x[u * D + c], ss);
+            ss = warp_sum(ss);
+            if (lane == 0) head_scale[u] = 1.0f / sqrtf(ss / (float)D + eps);
+        }
+        __syncthreads();
+    }
     const int half = rot_dim / 2;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    // q and k heads: a warp per head at a time; its lanes take pairs of channels
-    for (int u0 = 0; u0 < heads + kv_heads; u0 += nwarps) {
-        const int u = u0 + warp;
-        if (u < heads + kv_heads) {
-            const bool is_q = u < heads;
-            const int hd = is_q ? u : u - heads;
-            const float* xh = x + (is_q ? 0 : qw) + hd * D;
-            float sc = is_q ? q_scale : k_scale;
-            if (norm_mode == 1) {
-                float ss = 0.f;
-                for (int c = lane; c < D; c += 32) ss = fmaf(xh[c], xh[c], ss);
-                sc = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
+    // Channel c of the q | k stretch after norm and rotation. Its partner in the rotation is its neighbour (pairing 1)
+    // or the channel half the rotated part away (pairing 0); the first of a pair becomes u cos - v sin, the second
+    // v cos + u sin.
+    auto channel = [&](int c) -> float {
+        const bool is_q = c < qw;
+        const int cc = is_q ? c : c - qw;                       // column within the q or the k projection
+        const int u = c / D, d = c - u * D;                     // head among q and k heads, channel within it
+        const TW* w = is_q ? q_w : k_w;
+        const float sc = norm_mode == 2 ? (is_q ? q_scale : k_scale) : norm_mode == 1 ? head_scale[u] : 1.0f;
+        const int wi = norm_mode == 2 ? cc : d;
+        const float a = norm_mode ? x[c] * sc * to_f32(w[wi]) : x[c];
+        if (d >= rot_dim) return a;
+        const bool first = pairing ? !(d & 1) : d < half;
+        const int off = pairing ? (first ? 1 : -1) : (first ? half : -half);
+        const float b = norm_mode ? x[c + off] * sc * to_f32(w[wi + off]) : x[c + off];
+        const float2 t = turn[pairing ? d >> 1 : (first ? d : d - half)];
+        return first ? a * t.x - b * t.y : a * t.x + b * t.y;
+    };
+    T* k_row = page >= 0 ? k_pages + ((size_t)page * kv_heads * CML_PAGE + pos % CML_PAGE) * D : nullptr;
+    if ((D & 1) == 0) {                                          // two neighbouring channels a thread: 4-byte stores of bfloat16
+        for (int c = threadIdx.x * 2; c < qw + kw; c += blockDim.x * 2) {
+            const float o0 = channel(c), o1 = channel(c + 1);
+            T* o;
+            if (c < qw) o = q_out + (size_t)r * qw + c;
+            else {
+                if (k_row == nullptr) continue;
+                const int g = (c - qw) / D;
+                o = k_row + (size_t)g * CML_PAGE * D + (c - qw - g * D);
             }
-            const TW* w = is_q ? q_w : k_w;
-            const int woff = norm_mode == 2 ? hd * D : 0;
-            T* o = is_q ? q_out + ((size_t)r * heads + hd) * D
-                        : (page >= 0 ? k_pages + (((size_t)page * kv_heads + hd) * CML_PAGE + pos % CML_PAGE) * D : nullptr);
-            if (o != nullptr) {
-                for (int i = lane; i < half; i += 32) {
-                    const int c0 = pairing ? 2 * i : i, c1 = pairing ? 2 * i + 1 : i + half;
-                    float a = xh[c0], b = xh[c1];
-                    if (norm_mode) { a = a * sc * to_f32(w[woff + c0]); b = b * sc * to_f32(w[woff + c1]); }
-                    const float cs = turn[i].x, sn = turn[i].y;
-                    o[c0] = from_f32<T>(a * cs - b * sn);
-                    o[c1] = from_f32<T>(b * cs + a * sn);
-                }
-                for (int c = 2 * half + lane; c < D; c += 32)
-                    o[c] = from_f32<T>(norm_mode ? xh[c] * sc * to_f32(w[woff + c]) : xh[c]);
+            o[0] = from_f32<T>(o0);
+            o[1] = from_f32<T>(o1);
+        }
+    } else {
+        for (int c = threadIdx.x; c < qw + kw; c += blockDim.x) {
+            const float o0 = channel(c);
+            if (c < qw) q_out[(size_t)r * qw + c] = from_f32<T>(o0);
+            else if (k_row != nullptr) {
+                const int g = (c - qw) / D;
+                k_row[(size_t)g * CML_PAGE * D + (c - qw - g * D)] = from_f32<T>(o0);
             }
         }
     }
@@ -197,7 +218,7 @@ extern "C" int cml_qkv_prepare(const float* proj, long ld, int n_splits, long sp
     if (rot_dim < 0 || rot_dim > D || rot_dim > 256 || (rot_dim & 1) || norm_mode < 0 || norm_mode > 2) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (n_splits < 1 || extra < 0) return CML_ERR_BAD_SIZE;
-    const size_t smem = (size_t)(heads * D + kv_heads * (D + Dv) + extra) * sizeof(float);
+    const size_t smem = (size_t)(heads * D + kv_heads * (D + Dv) + extra + heads + kv_heads) * sizeof(float);
     if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
 #define QP_CASE(T_, TW_, D_, DW_)                                                                                          \
     if (dtype == D_ && w_dtype == DW_) {                                                                                   \

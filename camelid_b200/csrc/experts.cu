@@ -30,8 +30,8 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, long ld, int
     if (r >= rows) return;
     float* z = rt_z + (threadIdx.x >> 5) * E;
     for (int e = lane; e < E; e += 32) {
-        float v = 0.f;
-        for (int s0 = 0; s0 < n_splits; s0 += 8) {              // eight splits' loads in flight, added in split order
+        float v = logits[(size_t)r * ld + e];
+        for (int s0 = 1; s0 < n_splits; s0 += 8) {              // eight splits' loads in flight, added in split order
             float t[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) t[k] = logits[(size_t)min(s0 + k, n_splits - 1) * split_stride + (size_t)r * ld + e];

@@ -552,7 +552,7 @@ extern "C" int cml_norm_combine(const float* const* y, const void* const* w, con
 //   x_out[r] = h[r] / sqrt(mean(h[r]^2) + eps_next) * w_next     (if x_out is given)
 // One block per row; the row stays in shared memory between the passes; all sums in float.
 template <typename TW, typename TO>
-__global__ void __launch_bounds__(256) post_norm_add_kernel(const float* __restrict__ y, int n_splits, long split_stride,
+__global__ void __launch_bounds__(512) post_norm_add_kernel(const float* __restrict__ y, int n_splits, long split_stride,
                                                             const float* __restrict__ bias, const TW* __restrict__ w_post,
                                                             float eps, float coef, float* __restrict__ h,
                                                             const TW* __restrict__ w_next, float eps_next,
@@ -567,9 +567,16 @@ __global__ void __launch_bounds__(256) post_norm_add_kernel(const float* __restr
     if (vec) {
         for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
             float4 v = *reinterpret_cast<const float4*>(y + base + c);
-            for (int s = 1; s < n_splits; ++s) {
-                const float4 t = *reinterpret_cast<const float4*>(y + (size_t)s * split_stride + base + c);
-                v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+            // the other splits eight at a time: unconditional loads (of a valid place), all in flight before the first
+            // add; the adds stay in split order
+            for (int s0 = 1; s0 < n_splits; s0 += 8) {
+                float4 t[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    t[k] = *reinterpret_cast<const float4*>(y + (size_t)min(s0 + k, n_splits - 1) * split_stride + base + c);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (s0 + k < n_splits) { v.x += t[k].x; v.y += t[k].y; v.z += t[k].z; v.w += t[k].w; }
             }
             if (bias) { v.x += bias[c]; v.y += bias[c + 1]; v.z += bias[c + 2]; v.w += bias[c + 3]; }
             *reinterpret_cast<float4*>(pn_row + c) = v;
@@ -628,7 +635,8 @@ extern "C" int cml_post_norm_add(const float* y, int n_splits, long split_stride
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    const int block = hidden >= 1024 ? 256 : 128;
+    // few rows (one-token steps): more threads per row shorten each thread's chain of columns
+    const int block = rows <= 256 && hidden >= 2048 ? 512 : (hidden >= 1024 ? 256 : 128);
 #define PN_CASE(TW_, TO_, DW_, DO_)                                                                                        \
     if (w_dtype == DW_ && (x_out == nullptr || out_dtype == DO_)) {                                                        \
         if (smem > 48 * 1024 && cml_allow_smem<post_norm_add_kernel<TW_, TO_>>(smem) != cudaSuccess) return CML_ERR_BAD_SIZE; \

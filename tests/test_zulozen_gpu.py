@@ -362,6 +362,53 @@ def test_prompt_attention_on_tensor_cores_with_blocks_sink_and_gate(cuda, D, gro
         assert err < 3e-2, f"{what}: {err}"
 
 
+@pytest.mark.parametrize("norm_mode,interleaved,D,rot,splits", [(1, False, 12, 8, 1), (0, True, 16, 16, 3), (1, True, 7, 4, 2),
+                                                                 (2, False, 24, 24, 11), (0, False, 8, 0, 1)])
+def test_preparation_kernel_in_every_mode(cuda, norm_mode, interleaved, D, rot, splits):
+    """Norm per head, over the whole projection or none; pairs of neighbours or of halves; an odd head size; the input
+    as split sums; the gate's logits handed on."""
+    from camelid_b200.csrc import ops
+    gen = torch.Generator().manual_seed(9)
+    T, H, G, Dv, eps, base, extra = 70, 3, 1, 5, 1e-5, 100.0, 3
+    n = H * D + G * D + G * Dv + extra
+    parts = torch.randn(splits, T, n, generator=gen)
+    x = parts.double().sum(0).numpy()
+    wq = (1 + 0.3 * torch.randn(H * D if norm_mode == 2 else D, generator=gen))
+    wk = (1 + 0.3 * torch.randn(G * D if norm_mode == 2 else D, generator=gen))
+    q, k = x[:, :H * D], x[:, H * D:(H + G) * D]
+    if norm_mode == 2:
+        q, k = pz.rms_norm(q, wq.double().numpy(), eps), pz.rms_norm(k, wk.double().numpy(), eps)
+    q, k = q.reshape(T, H, D), k.reshape(T, G, D)
+    if norm_mode == 1:
+        q, k = pz.rms_norm(q, wq.double().numpy(), eps), pz.rms_norm(k, wk.double().numpy(), eps)
+    pos = np.arange(T)
+
+    def turn(t):
+        if not rot:
+            return t
+        if interleaved:
+            return pz.rotate_interleaved(t, pos, rot, base)
+        out, half = t.copy(), rot // 2
+        ang = pos[:, None] * base ** (-2.0 * np.arange(half) / rot)[None, :]
+        c, sn = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+        out[..., :half] = t[..., :half] * c - t[..., half:rot] * sn
+        out[..., half:rot] = t[..., half:rot] * c + t[..., :half] * sn
+        return out
+    q, k = turn(q), turn(k)
+    inv_freq = torch.tensor([base ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float32, device=cuda)
+    table, kp, vp = _paged(cuda, T, G, D, Dv, torch.float32)
+    a = arrays(cuda, [0], [T])
+    qo, gate = torch.empty(T, H * D, device=cuda), torch.empty(T, extra, device=cuda)
+    ops.qkv_prepare(parts.to(cuda), wq.to(cuda) if norm_mode else None, wk.to(cuda) if norm_mode else None, norm_mode, eps, inv_freq,
+                    rot, interleaved, a["row_seq"], a["row_pos"], table, qo, kp, vp, H, G, D, Dv, gate)
+    assert np.allclose(qo.cpu().double().numpy(), q.reshape(T, -1), atol=2e-5)
+    assert np.allclose(gate.cpu().double().numpy(), x[:, -extra:], atol=2e-5)
+    tb = table.cpu()[0]
+    for t in (0, 63, 64, T - 1):
+        assert np.allclose(kp[tb[t // 64], :, t % 64].cpu().double().numpy(), k[t], atol=2e-5)
+        assert np.allclose(vp[tb[t // 64], :, t % 64].cpu().double().numpy(), x[t, (H + G) * D:(H + G) * D + G * Dv].reshape(G, Dv), atol=2e-5)
+
+
 def test_sink_alone_takes_its_share(cuda):
     """One key of score zero and a sink of ln 3: the key's value comes out at a quarter."""
     from camelid_b200.csrc import ops
