@@ -554,7 +554,7 @@ def zulozen_config_for(size: str) -> dict:
                {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "router": {"experts": s["experts"], "top": s["top"]},
                 "shared": {"ff": s["shared_ff"]}})
         layers.append({"type": "attention", "mixer": dict(mixer), "mlp": mlp})
-    return {"architecture": "Zulozen", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.3,
+    return {"architecture": "Zulozen", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.5,
             "layers": layers}
 
 

@@ -502,16 +502,16 @@ def test_dense_feed_forward_and_the_norm_behind_it(cuda):
     assert torch.allclose(whole.cpu().double(), ref, atol=1e-5)
     y, b, w = torch.randn(2, rows, W, generator=gen), torch.randn(W, generator=gen), 1 + 0.3 * torch.randn(W, generator=gen)
     stream = torch.randn(rows, W, generator=gen)
-    want = stream.double() + 0.3 * torch.from_numpy(pz.rms_norm((y.double().sum(0) + b.double()).numpy(), w.double().numpy(), 1e-5))
+    want = stream.double() + 0.35 * torch.from_numpy(pz.rms_norm((y.double().sum(0) + b.double()).numpy(), w.double().numpy(), 1e-5))
     s = stream.to(cuda)
-    ops.norm_combine([(y.to(cuda), w.to(cuda))], s, 1e-5, 0.3, [b.to(cuda)])
+    ops.norm_combine([(y.to(cuda), w.to(cuda))], s, 1e-5, 0.35, [b.to(cuda)])
     assert torch.allclose(s.cpu().double(), want, atol=1e-5)
     # the same in one pass with the norm that follows; a width that allows no 16-byte pieces too
     for width in (W, W - 3):
         w2 = 1 + 0.3 * torch.randn(width, generator=gen)
         yy, bb, ww, st = y[:, :, :width].contiguous(), b[:width].contiguous(), w[:width].contiguous(), stream[:, :width].contiguous()
-        want = st.double() + 0.3 * torch.from_numpy(pz.rms_norm((yy.double().sum(0) + bb.double()).numpy(), ww.double().numpy(), 1e-5))
+        want = st.double() + 0.35 * torch.from_numpy(pz.rms_norm((yy.double().sum(0) + bb.double()).numpy(), ww.double().numpy(), 1e-5))
         want_x = torch.from_numpy(pz.rms_norm(want.numpy(), w2.double().numpy(), 2e-5))
         s2, x = st.to(cuda), torch.empty(rows, width, device=cuda)
-        ops.post_norm_add(yy.to(cuda), bb.to(cuda), ww.to(cuda), 1e-5, 0.3, s2, w2.to(cuda), 2e-5, x)
+        ops.post_norm_add(yy.to(cuda), bb.to(cuda), ww.to(cuda), 1e-5, 0.35, s2, w2.to(cuda), 2e-5, x)
         assert torch.allclose(s2.cpu().double(), want, atol=1e-5) and torch.allclose(x.cpu().double(), want_x, atol=1e-5)
