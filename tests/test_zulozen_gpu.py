@@ -331,14 +331,11 @@ def test_prompt_attention_on_tensor_cores_with_blocks_sink_and_gate(cuda, D, gro
     vp = torch.zeros_like(kp)
     dev = lambda x: torch.tensor(x, dtype=torch.int32, device=cuda)      # noqa: E731
     # the earlier part of the first sequence is in the cache already; then the step's rows
-    for seq_rows, st, n in ((0, 0, starts[0]), (None, None, None)):
-        if seq_rows == 0:
-            a = arrays(cuda, [0], [starts[0]])
-            a["row_seq"].zero_()
-            sl = [slice(0, starts[0]), None]
-            proj = torch.cat([qs[0][sl[0]].reshape(starts[0], -1), ks[0][sl[0]].reshape(starts[0], -1), vs[0][sl[0]].reshape(starts[0], -1)], 1)
-            ops.qk_norm_kv_write(proj.float().to(cuda), None, None, 1e-6, a["row_seq"], a["row_pos"], table,
-                                 torch.empty(starts[0], H * D, dtype=torch.bfloat16, device=cuda), kp, vp, H, G, D, D)
+    n0 = starts[0]
+    early = arrays(cuda, [0], [n0])
+    proj = torch.cat([qs[0][:n0].reshape(n0, -1), ks[0][:n0].reshape(n0, -1), vs[0][:n0].reshape(n0, -1)], 1).float().to(cuda)
+    ops.qk_norm_kv_write(proj, None, None, 1e-6, early["row_seq"], early["row_pos"], table,
+                         torch.empty(n0, H * D, dtype=torch.bfloat16, device=cuda), kp, vp, H, G, D, D)
     a = arrays(cuda, starts, lens)
     rows = sum(lens)
     cat = lambda xs: torch.cat([x[st:].reshape(t - st, -1) for x, t, st in zip(xs, total, starts)])      # noqa: E731
