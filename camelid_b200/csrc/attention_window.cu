@@ -96,28 +96,70 @@ extern "C" int cml_qk_norm_kv_write(const float* proj, long ld, const void* q_w,
 // projection (heads x D channels at once) and the whole k projection, weights of those sizes. Then the first
 // rot_dim channels of every q and k head are rotated by angle = position * inv_freq[i] (float), pairing 1:
 // channels (2i, 2i + 1); pairing 0: channels (i, i + rot_dim / 2). One block per row. proj may come as split sums
-// (n_splits matrices split_stride apart, added here in split order); the row is staged in shared memory. `extra`
-// more columns behind v (the logits of an output gate) are copied, summed, to extra_out [rows, extra].
-template <typename T, typename TW>
-__global__ void __launch_bounds__(1024) qkv_prepare_kernel(const float* __restrict__ proj, long ld, int n_splits, long split_stride,
-                                   int extra, float* __restrict__ extra_out, const TW* __restrict__ q_w,
-                                   const TW* __restrict__ k_w, int norm_mode, float eps, const float* __restrict__ inv_freq,
-                                   int rot_dim, int pairing, const int* __restrict__ row_seq, const int* __restrict__ row_pos,
-                                   const int* __restrict__ table, int max_blocks, T* __restrict__ q_out, T* __restrict__ k_pages,
-                                   T* __restrict__ v_pages, int heads, int kv_heads, int D, int Dv) {
-    __shared__ float red[33];
+// (n_splits matrices split_stride apart, added here in split order); the row is staged in shared memory, its sums
+// of squares taken on the way in. `extra` more columns behind v (the logits of an output gate) are copied, summed,
+// to extra_out [rows, extra]. A warp works on one head at a time, a lane on four neighbouring channels (two, or
+// one, where the head size allows no more), so that a warp's stores are one contiguous run.
+template <typename T> __device__ __forceinline__ void store_run(T* o, const float* v, int n);
+template <> __device__ __forceinline__ void store_run<float>(float* o, const float* v, int n) {
+    if (n == 4) *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+    else if (n == 2) *reinterpret_cast<float2*>(o) = make_float2(v[0], v[1]);
+    else o[0] = v[0];
+}
+template <> __device__ __forceinline__ void store_run<bf16>(bf16* o, const float* v, int n) {
+    if (n == 4) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(o) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    } else if (n == 2) {
+        *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(v[0], v[1]);
+    } else {
+        o[0] = __float2bfloat16_rn(v[0]);
+    }
+}
+
+template <typename T, typename TW, int THREADS>
+__global__ void __launch_bounds__(THREADS, THREADS <= 256 ? 5 : 1)
+qkv_prepare_kernel(const float* __restrict__ proj, long ld, int n_splits, long split_stride, int extra,
+                   float* __restrict__ extra_out, const TW* __restrict__ q_w, const TW* __restrict__ k_w, int norm_mode, float eps,
+                   const float* __restrict__ inv_freq, int rot_dim, int pairing, const int* __restrict__ row_seq,
+                   const int* __restrict__ row_pos, const int* __restrict__ table, int max_blocks, T* __restrict__ q_out,
+                   T* __restrict__ k_pages, T* __restrict__ v_pages, int heads, int kv_heads, int D, int Dv) {
+    __shared__ float red[2][32];
     __shared__ float2 turn[128];                                // (cosine, sine) of the row's angles, shared by all heads
+    extern __shared__ __align__(16) float x[];                 // the row: q, k, v, the extra columns
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ __align__(16) float x[];                 // the row: q, k, v and the extra columns
     const int r = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int NWARPS = THREADS / 32;
     const int qw = heads * D, kw = kv_heads * D, vw = kv_heads * Dv;
-    {
-        const float* src = proj + (size_t)r * ld;
-        const int total = qw + kw + vw + extra;
-        for (int c = threadIdx.x; c < total; c += blockDim.x) {
-            // eight splits at a time: the loads are unconditional (of a valid place) and all in flight before the
-            // first add; the adds stay in split order
+    const int total = qw + kw + vw + extra;
+    const float* src = proj + (size_t)r * ld;
+    float sq = 0.f, sk = 0.f;                                   // sums of squares of the q and the k columns
+    if (((ld | split_stride | (long)total) & 3) == 0 && (((uintptr_t)proj) & 15) == 0) {
+        for (int c = threadIdx.x * 4; c < total; c += THREADS * 4) {
+            float4 v = *reinterpret_cast<const float4*>(src + c);
+            // the other splits eight at a time: unconditional loads (of a valid place), all in flight before the first
+            // add; the adds stay in split order
+            for (int s0 = 1; s0 < n_splits; s0 += 8) {
+                float4 t[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    t[k] = *reinterpret_cast<const float4*>(src + (size_t)min(s0 + k, n_splits - 1) * split_stride + c);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (s0 + k < n_splits) { v.x += t[k].x; v.y += t[k].y; v.z += t[k].z; v.w += t[k].w; }
+            }
+            *reinterpret_cast<float4*>(x + c) = v;
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (c + i < qw) sq = fmaf(e[i], e[i], sq);
+                else if (c + i < qw + kw) sk = fmaf(e[i], e[i], sk);
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < total; c += THREADS) {
             float v = src[c];
             for (int s0 = 1; s0 < n_splits; s0 += 8) {
                 float t[8];
@@ -127,113 +169,130 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(const float* __restri
                 for (int k = 0; k < 8; ++k) v += s0 + k < n_splits ? t[k] : 0.f;
             }
             x[c] = v;
-            if (c >= total - extra) extra_out[(size_t)r * extra + (c - (total - extra))] = v;
+            if (c < qw) sq = fmaf(v, v, sq);
+            else if (c < qw + kw) sk = fmaf(v, v, sk);
         }
     }
     const int pos = row_pos[r];
-    for (int i = threadIdx.x; i < rot_dim / 2; i += blockDim.x) {
+    const int page = table[(size_t)row_seq[r] * max_blocks + pos / CML_PAGE];
+    for (int i = threadIdx.x; i < rot_dim / 2; i += THREADS) {
         float sn, cs;
         sincosf((float)pos * inv_freq[i], &sn, &cs);
         turn[i] = make_float2(cs, sn);
     }
+    if (norm_mode == 2) {                                       // both sums over the block with one barrier
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        if (lane == 0) { red[0][warp] = sq; red[1][warp] = sk; }
+    }
     __syncthreads();
-    const int page = table[(size_t)row_seq[r] * max_blocks + pos / CML_PAGE];
     float q_scale = 1.0f, k_scale = 1.0f;
     if (norm_mode == 2) {
-        float sq = 0.f, sk = 0.f;
-        for (int c = threadIdx.x; c < qw; c += blockDim.x) sq = fmaf(x[c], x[c], sq);
-        for (int c = threadIdx.x; c < kw; c += blockDim.x) sk = fmaf(x[qw + c], x[qw + c], sk);
-        q_scale = 1.0f / sqrtf(block_sum(sq, red) / (float)qw + eps);
-        __syncthreads();
-        k_scale = 1.0f / sqrtf(block_sum(sk, red) / (float)kw + eps);
-        __syncthreads();
+        q_scale = 1.0f / sqrtf(warp_sum(lane < NWARPS ? red[0][lane] : 0.f) / (float)qw + eps);
+        k_scale = 1.0f / sqrtf(warp_sum(lane < NWARPS ? red[1][lane] : 0.f) / (float)kw + eps);
     }
-    float* head_scale = x + qw + kw + vw + extra;               // norm per head: one scale per q and k head
-    if (norm_mode == 1) {
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-        for (int u = warp; u < heads + kv_heads; u += nwarps) {
-            float ss = 0.f;
-            for (int c = lane; c < D; c += 32) ss = fmaf(x[u * D + c], x[u * D + c], ss);
-            ss = warp_sum(ss);
-            if (lane == 0) head_scale[u] = 1.0f / sqrtf(ss / (float)D + eps);
-        }
-        __syncthreads();
-    }
+    for (int c = threadIdx.x; c < extra; c += THREADS) extra_out[(size_t)r * extra + c] = x[total - extra + c];
     const int half = rot_dim / 2;
-    // Channel c of the q | k stretch after norm and rotation. Its partner in the rotation is its neighbour (pairing 1)
-    // or the channel half the rotated part away (pairing 0); the first of a pair becomes u cos - v sin, the second
-    // v cos + u sin.
-    auto channel = [&](int c) -> float {
-        const bool is_q = c < qw;
-        const int cc = is_q ? c : c - qw;                       // column within the q or the k projection
-        const int u = c / D, d = c - u * D;                     // head among q and k heads, channel within it
-        const TW* w = is_q ? q_w : k_w;
-        const float sc = norm_mode == 2 ? (is_q ? q_scale : k_scale) : norm_mode == 1 ? head_scale[u] : 1.0f;
-        const int wi = norm_mode == 2 ? cc : d;
-        const float a = norm_mode ? x[c] * sc * to_f32(w[wi]) : x[c];
-        if (d >= rot_dim) return a;
-        const bool first = pairing ? !(d & 1) : d < half;
-        const int off = pairing ? (first ? 1 : -1) : (first ? half : -half);
-        const float b = norm_mode ? x[c + off] * sc * to_f32(w[wi + off]) : x[c + off];
-        const float2 t = turn[pairing ? d >> 1 : (first ? d : d - half)];
-        return first ? a * t.x - b * t.y : a * t.x + b * t.y;
-    };
     T* k_row = page >= 0 ? k_pages + ((size_t)page * kv_heads * CML_PAGE + pos % CML_PAGE) * D : nullptr;
-    if ((D & 1) == 0) {                                          // two neighbouring channels a thread: 4-byte stores of bfloat16
-        for (int c = threadIdx.x * 2; c < qw + kw; c += blockDim.x * 2) {
-            const float o0 = channel(c), o1 = channel(c + 1);
-            T* o;
-            if (c < qw) o = q_out + (size_t)r * qw + c;
-            else {
-                if (k_row == nullptr) continue;
-                const int g = (c - qw) / D;
-                o = k_row + (size_t)g * CML_PAGE * D + (c - qw - g * D);
-            }
-            o[0] = from_f32<T>(o0);
-            o[1] = from_f32<T>(o1);
+    const int run = (D & 3) == 0 ? 4 : (D & 1) == 0 ? 2 : 1;     // neighbouring channels a lane takes
+    for (int u = warp; u < heads + kv_heads; u += NWARPS) {
+        const bool is_q = u < heads;
+        const int hd = is_q ? u : u - heads;
+        const float* xh = x + u * D;
+        float sc = is_q ? q_scale : k_scale;
+        if (norm_mode == 1) {                                   // the head's own scale
+            float ss = 0.f;
+            for (int c = lane; c < D; c += 32) ss = fmaf(xh[c], xh[c], ss);
+            sc = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
         }
-    } else {
-        for (int c = threadIdx.x; c < qw + kw; c += blockDim.x) {
-            const float o0 = channel(c);
-            if (c < qw) q_out[(size_t)r * qw + c] = from_f32<T>(o0);
-            else if (k_row != nullptr) {
-                const int g = (c - qw) / D;
-                k_row[(size_t)g * CML_PAGE * D + (c - qw - g * D)] = from_f32<T>(o0);
+        const TW* w = (is_q ? q_w : k_w) + (norm_mode == 2 ? hd * D : 0);
+        T* o = is_q ? q_out + (size_t)r * qw + hd * D : (k_row != nullptr ? k_row + (size_t)hd * CML_PAGE * D : nullptr);
+        if (o == nullptr) continue;
+        // channel d of the head after the norm
+        auto normed = [&](int d) -> float { return norm_mode ? xh[d] * sc * to_f32(w[d]) : xh[d]; };
+        for (int d = run * lane; d < D; d += run * 32) {
+            float out[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) out[i] = i < run ? normed(d + i) : 0.f;
+            if (d < rot_dim) {
+                if (pairing && run > 1) {                       // neighbours are each other's partners
+#pragma unroll
+                    for (int i = 0; i < 4; i += 2) {
+                        if (i < run && d + i < rot_dim) {
+                            const float2 t = turn[(d + i) >> 1];
+                            const float a = out[i], b = out[i + 1];
+                            out[i] = a * t.x - b * t.y;
+                            out[i + 1] = b * t.x + a * t.y;
+                        }
+                    }
+                } else {                                        // the partner is elsewhere in the head: fetched and normed again
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int c = d + i;
+                        if (i < run && c < rot_dim) {
+                            const bool first = pairing ? !(c & 1) : c < half;
+                            const int other = pairing ? (first ? c + 1 : c - 1) : (first ? c + half : c - half);
+                            const float2 t = turn[pairing ? c >> 1 : (first ? c : c - half)];
+                            const float b = normed(other);
+                            out[i] = first ? out[i] * t.x - b * t.y : out[i] * t.x + b * t.y;
+                        }
+                    }
+                }
             }
+            store_run<T>(o + d, out, run);
         }
     }
     if (page >= 0) {
-        for (int c = threadIdx.x; c < vw; c += blockDim.x) {
-            const int g = c / Dv, e = c - g * Dv;
-            v_pages[(((size_t)page * kv_heads + g) * CML_PAGE + pos % CML_PAGE) * Dv + e] = from_f32<T>(x[qw + kw + c]);
+        T* v_row = v_pages + ((size_t)page * kv_heads * CML_PAGE + pos % CML_PAGE) * Dv;
+        const float* xv = x + qw + kw;
+        if ((Dv & 3) == 0 && ((qw + kw) & 3) == 0) {
+            for (int c = threadIdx.x * 4; c < vw; c += THREADS * 4) {
+                const int g = c / Dv, e = c - g * Dv;
+                const float4 v = *reinterpret_cast<const float4*>(xv + c);
+                const float vals[4] = {v.x, v.y, v.z, v.w};
+                store_run<T>(v_row + (size_t)g * CML_PAGE * Dv + e, vals, 4);
+            }
+        } else {
+            for (int c = threadIdx.x; c < vw; c += THREADS) {
+                const int g = c / Dv, e = c - g * Dv;
+                v_row[(size_t)g * CML_PAGE * Dv + e] = from_f32<T>(xv[c]);
+            }
         }
     }
 }
 
-extern "C" int cml_qkv_prepare(const float* proj, long ld, int n_splits, long split_stride, int extra, float* extra_out, const void* q_w, const void* k_w, int w_dtype, int norm_mode, float eps,
-                               const float* inv_freq, int rot_dim, int pairing, const int* row_seq, const int* row_pos,
-                               const int* table, int max_blocks, void* q_out, void* k_pages, void* v_pages, int dtype, int rows,
-                               int heads, int kv_heads, int D, int Dv, void* stream) {
+extern "C" int cml_qkv_prepare(const float* proj, long ld, int n_splits, long split_stride, int extra, float* extra_out,
+                               const void* q_w, const void* k_w, int w_dtype, int norm_mode, float eps, const float* inv_freq,
+                               int rot_dim, int pairing, const int* row_seq, const int* row_pos, const int* table,
+                               int max_blocks, void* q_out, void* k_pages, void* v_pages, int dtype, int rows, int heads,
+                               int kv_heads, int D, int Dv, void* stream) {
     if (rows <= 0) return 0;
     if (rot_dim < 0 || rot_dim > D || rot_dim > 256 || (rot_dim & 1) || norm_mode < 0 || norm_mode > 2) return CML_ERR_BAD_SIZE;
-    cudaStream_t s = (cudaStream_t)stream;
     if (n_splits < 1 || extra < 0) return CML_ERR_BAD_SIZE;
-    const size_t smem = (size_t)(heads * D + kv_heads * (D + Dv) + extra + heads + kv_heads) * sizeof(float);
+    // the vector stores want aligned rows: the outputs' bases come 16-byte aligned from the allocator, the sizes decide the rest
+    if ((((uintptr_t)q_out) | ((uintptr_t)k_pages) | ((uintptr_t)v_pages)) & 15) return CML_ERR_BAD_ALIGN;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)(heads * D + kv_heads * (D + Dv) + extra + 4) * sizeof(float);
     if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
+    const bool few = rows <= 128;                               // one-token steps: more threads per row
+#define QP_LAUNCH(T_, TW_, N_)                                                                                             \
+    {                                                                                                                      \
+        if (smem > 48 * 1024 && cml_allow_smem<qkv_prepare_kernel<T_, TW_, N_>>(smem) != cudaSuccess) return CML_ERR_BAD_SIZE; \
+        launch_pdl(qkv_prepare_kernel<T_, TW_, N_>, dim3(rows), dim3(N_), smem, s, proj, ld, n_splits, split_stride, extra, \
+                   extra_out, (const TW_*)q_w, (const TW_*)k_w, norm_mode, eps, inv_freq, rot_dim, pairing, row_seq, row_pos, \
+                   table, max_blocks, (T_*)q_out, (T_*)k_pages, (T_*)v_pages, heads, kv_heads, D, Dv);                      \
+        return cml_launch_status();                                                                                        \
+    }
 #define QP_CASE(T_, TW_, D_, DW_)                                                                                          \
     if (dtype == D_ && w_dtype == DW_) {                                                                                   \
-        if (smem > 48 * 1024 && cml_allow_smem<qkv_prepare_kernel<T_, TW_>>(smem) != cudaSuccess) return CML_ERR_BAD_SIZE; \
-        launch_pdl(qkv_prepare_kernel<T_, TW_>, dim3(rows), dim3(rows <= 128 ? 1024 : 256), smem, s, proj, ld, n_splits, split_stride, extra,   \
-                   extra_out, (const TW_*)q_w, (const TW_*)k_w,                                                            \
-                   norm_mode, eps, inv_freq, rot_dim, pairing, row_seq, row_pos, table, max_blocks, (T_*)q_out,            \
-                   (T_*)k_pages, (T_*)v_pages, heads, kv_heads, D, Dv);                                                    \
-        return cml_launch_status();                                                                                        \
+        if (few) QP_LAUNCH(T_, TW_, 1024) else QP_LAUNCH(T_, TW_, 256)                                                     \
     }
     QP_CASE(float, float, CML_DTYPE_F32, CML_DTYPE_F32)
     QP_CASE(bf16, bf16, CML_DTYPE_BF16, CML_DTYPE_BF16)
     QP_CASE(bf16, float, CML_DTYPE_BF16, CML_DTYPE_F32)
     QP_CASE(float, bf16, CML_DTYPE_F32, CML_DTYPE_BF16)
 #undef QP_CASE
+#undef QP_LAUNCH
     return CML_ERR_BAD_DTYPE;
 }
 
