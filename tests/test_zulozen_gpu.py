@@ -19,8 +19,8 @@ from helpers import assert_same_engine, tokens
 
 pytestmark = pytest.mark.gpu
 
-SEEDS = {"mixed": 21, "odd": 22, "wide": 23, "open": 24}
-LENGTHS = {"mixed": 150, "odd": 141, "wide": 270, "open": 90}
+SEEDS = {"mixed": 21, "odd": 22, "wide": 23, "open": 24, "all_experts": 25}
+LENGTHS = {"mixed": 150, "odd": 141, "wide": 270, "open": 90, "all_experts": 330}
 
 
 @pytest.fixture(scope="module")
@@ -63,6 +63,8 @@ def assert_close(got, ref_and_margin, dtype, what=""):
     before the first near tie of the sequence, and of all rows together that most of them keep it."""
     ref, margin = ref_and_margin
     got = torch.as_tensor(got)
+    if dtype == "bfloat16" and np.isinf(margin).all():          # no choice to make anywhere: every row counts
+        return helpers.assert_close(got, ref, dtype, what)
     if dtype == "bfloat16":
         clear = np.minimum.accumulate(margin) > 0.05
         rows = helpers.row_errors(got, ref)
