@@ -78,3 +78,27 @@ def test_more_than_one_gpu_is_refused_with_one_line():
     assert r.returncode == 2 and len(r.stdout.strip().splitlines()) == 1 and "single-GPU" in r.stdout
     r = _bench("--gpus", "2", env={"WORLD_SIZE": "2", "RANK": "1"})
     assert r.returncode == 2 and r.stdout.strip() == ""        # only rank 0 speaks
+
+
+def test_zulozen_shapes_and_counts():
+    """The sizes `bench.py --zulozen` names are whole configurations whose routed layers pass as many feed-forward
+    elements per token as the dense ones; the byte and operation counts of a hand-sized model."""
+    from camelid_b200.config.registry import load_config
+    for size, s in benchmark.ZULOZEN_SIZES.items():
+        cfg = benchmark.zulozen_config_for(size)
+        _arch, typed, plan = load_config(cfg)
+        assert len(plan.layers) == s["layers"] and typed.width == s["width"]
+        assert s["top"] * s["expert_ff"] + s["shared_ff"] == s["ff"]
+        like = benchmark.llama_config_like_zulozen(size)
+        assert (like["hidden_size"], like["num_hidden_layers"], like["intermediate_size"]) == (s["width"], s["layers"], s["ff"])
+    mixer = {"dim": 8, "vdim": 4, "heads": 2, "kv_heads": 1, "mask": {"size": 3}, "scale": 1.0}
+    cfg = {"width": 16, "vocab": 10, "layers": [
+        {"mixer": mixer, "mlp": {"kind": "dense", "ff": 32}},
+        {"mixer": mixer, "mlp": {"kind": "moe", "expert": {"ff": 8}, "router": {"experts": 4, "top": 4}, "shared": {"ff": 6}}}]}
+    attn = 16 * (2 * 8 + 8 + 4 + 2) + 2 * 4 * 16            # q, k, v, gate rows; output
+    dense, routed = 2 * 16 * 32, 16 * 4 + 3 * 16 * (4 * 8 + 6)
+    # 5 tokens in blocks of 3 see 1, 2, 3, 1, 2 keys
+    want = 2.0 * 5 * (2 * attn + dense + routed) + 2 * (2.0 * 9 * 2 * (8 + 4)) + 2.0 * 16 * 10
+    assert benchmark.zulozen_prefill_flops(cfg, 5) == want
+    b = benchmark.zulozen_step_bytes(cfg, 3, 7.0, 2)        # every row takes all 4 experts; position 7 sees 7 mod 3 + 1 keys
+    assert b["weights"] == 2 * (2 * attn + dense + routed + 10 * 16) and b["kv"] == 2 * 2 * (3 * 2 * 1 * (8 + 4))
